@@ -104,6 +104,9 @@ class SequenceCache:
                 request = group.request
                 shape = (len(group.owners), total_pages + 1, request.kv_heads, page_tokens)
                 group.k = torch.zeros((*shape, request.head_dim), dtype=dtype, device=device)
+                if request.shared_values:
+                    group.v = group.k               # the values are (the head of) the keys: nothing of their own is kept
+                    continue
                 group.v = torch.zeros((shape[0], shape[1], request.v_heads or request.kv_heads, page_tokens,
                                        request.v_head_dim or request.head_dim), dtype=dtype, device=device)
             for key, request in self._state_requests.items():
@@ -148,7 +151,7 @@ class SequenceCache:
         total = 0
         for group in self.groups:
             if group.k is not None:
-                total += (group.k.numel() + group.v.numel()) * group.k.element_size()
+                total += (group.k.numel() + (0 if group.request.shared_values else group.v.numel())) * group.k.element_size()
         for state in self._state_of.values():
             total += state.numel() * state.element_size()
         return total
@@ -156,5 +159,6 @@ class SequenceCache:
     def token_bytes(self) -> int:
         """Bytes of keys and values one cached token occupies over all full-attention entries."""
         size = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.owners) * (g.request.kv_heads * g.request.head_dim + (g.request.v_heads or g.request.kv_heads) *
-                                    (g.request.v_head_dim or g.request.head_dim)) * size for g in self.groups)
+        return sum(len(g.owners) * (g.request.kv_heads * g.request.head_dim + (0 if g.request.shared_values else
+                                    (g.request.v_heads or g.request.kv_heads) * (g.request.v_head_dim or g.request.head_dim))) * size
+                   for g in self.groups)

@@ -2,6 +2,7 @@ from .spec import LayerCall, LayerSpec, ModelSpec, PartSpec
 from .qwen3 import ConfigError, Qwen3Config
 from .lederax import LederaxConfig
 from .vunepel import VunepelConfig
+from .bisodra import BisodraConfig
 from .registry import (
     config_from_dict,
     load_config,
@@ -15,9 +16,10 @@ from .registry import (
 register_architecture("Qwen3ForCausalLM", Qwen3Config, model_type="qwen3")
 register_architecture("Lederax", LederaxConfig)
 register_architecture("Vunepel", VunepelConfig)
+register_architecture("Bisodra", BisodraConfig)
 
 __all__ = [
-    "ConfigError", "LayerCall", "LayerSpec", "LederaxConfig", "ModelSpec", "PartSpec", "Qwen3Config", "VunepelConfig",
+    "BisodraConfig", "ConfigError", "LayerCall", "LayerSpec", "LederaxConfig", "ModelSpec", "PartSpec", "Qwen3Config", "VunepelConfig",
     "config_from_dict", "load_config", "load_config_dict", "load_preset", "preset_names",
     "register_architecture", "registered_architectures",
 ]

@@ -8,7 +8,10 @@
 // with the logarithm of the distance, computed in float like the score itself.  With `chunk` > 0 key j is visible
 // only if j / chunk == p / chunk as well (positions counted from the start of the sequence).  The value cache may
 // have fewer heads than the key cache: `nv` value heads, key head g reading value head g % nv (several score maps
-// over one set of values).
+// over one set of values).  With `r1` alone the penalty is linear, r1_h * (p - j).  With `keep_first` > 0 a windowed
+// query also sees the keys at positions below `keep_first`, at their true distances.  With `sink` the softmax has one
+// more term of score 0 that carries no value: p_j = exp(s_j) / (1 + sum exp(s_j)).  `v_row` is the length of a value
+// row in the value cache where it is longer than `dv` (values that are the leading elements of the cached keys).
 //
 // Counterparts in luozoupi/Qwen-Triton: kernels/flash_attention.py:54-152 (one kernel for both
 // cases, no split, no window) and the masked SDPA branch of modules/attention.py:110-123 with
@@ -34,9 +37,23 @@ struct AttnParams {
     const float* r2;
     int chunk;            // > 0: a query sees only the keys of its own chunk of this many positions, counted from position 0
     int nv;               // value heads: the values of key head g are those of value head g % nv (nv = nkv: its own)
+    int keep_first;       // > 0 with a window: keys at positions below this stay visible
+    int sink;             // 1: one more softmax term of score 0 without a value
+    int v_row;            // elements between the value rows of neighbouring tokens (dv unless the rows are longer)
 };
 
-__device__ __forceinline__ float distance_penalty(float r1, float r2, int distance) { return r1 * logf(1.f + r2 * (float)distance); }
+// r2 < 0 marks the linear form r1 * distance
+__device__ __forceinline__ float distance_penalty(float r1, float r2, int distance) {
+    return r2 < 0.f ? r1 * (float)distance : r1 * logf(1.f + r2 * (float)distance);
+}
+
+// Result of a softmax row with a sink term of score 0: the factor on the accumulator and the denominator, from the
+// running maximum m and sum l (both relative to m).  Formed around max(m, 0) so that neither exponential overflows.
+__device__ __forceinline__ void with_sink(float m, float& l, float& factor) {
+    const float top = fmaxf(m, 0.f);
+    factor = expf(m - top);
+    l = l * factor + expf(-top);
+}
 
 // ----------------------------------------------------------------------------- many tokens per sequence
 constexpr int PF_BQ = 16;       // queries per block
@@ -69,7 +86,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(const 
     const T* kc = (const T*)p.k_cache;
     const T* vc = (const T*)p.v_cache;
     const bool penalised = p.r1 != nullptr;
-    const float r1 = penalised ? p.r1[head] : 0.f, r2 = penalised ? p.r2[head] : 0.f;
+    const float r1 = penalised ? p.r1[head] : 0.f, r2 = penalised ? (p.r2 ? p.r2[head] : -1.f) : 0.f;
 
     for (int r = warp; r < PF_BQ; r += PF_WARPS)
         for (int c = lane; c < d; c += 32)
@@ -87,13 +104,17 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(const 
     int key_lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
     if (p.chunk > 0) key_lo = max(key_lo, p_first / p.chunk * p.chunk);
     const int vh = kvh % p.nv;
-    for (int k0 = key_lo; k0 <= p_last; k0 += PF_BK) {
+    // two ranges of keys: the kept first ones that lie before the window of the block's first row, then the window
+    const int keep_end = (p.window > 0 && p.keep_first > 0) ? min(p.keep_first, key_lo) : 0;
+    for (int range = keep_end > 0 ? 0 : 1; range < 2; ++range) {
+    const int range_lo = range == 0 ? 0 : key_lo, range_hi = range == 0 ? keep_end : p_last + 1;
+    for (int k0 = range_lo; k0 < range_hi; k0 += PF_BK) {
         __syncthreads();
         for (int r = warp; r < PF_BK; r += PF_WARPS) {
             const int key = k0 + r;
-            if (key <= p_last) {
+            if (key < range_hi) {
                 const size_t off = cache_offset(table, key, p.ring_tokens, p.page_tokens, p.nkv, kvh, d);
-                const size_t voff = cache_offset(table, key, p.ring_tokens, p.page_tokens, p.nv, vh, dv);
+                const size_t voff = cache_offset(table, key, p.ring_tokens, p.page_tokens, p.nv, vh, p.v_row);
                 for (int c = lane; c < d; c += 32) ks[r * kstride + c] = to_float(kc[off + c]);
                 for (int c = lane; c < dv; c += 32) vs[r * dv + c] = to_float(vc[voff + c]);
             } else {
@@ -109,7 +130,8 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(const 
             const int pos = past + q0 + r;
             float s = 0.f;
             for (int c = 0; c < d; ++c) s += qs[r * d + c] * ks[lane * kstride + c];
-            const bool visible = r < rows && key <= pos && (p.window <= 0 || key > pos - p.window) &&
+            const bool visible = r < rows && key < range_hi && key <= pos &&
+                                 (p.window <= 0 || key > pos - p.window || key < p.keep_first) &&
                                  (p.chunk <= 0 || key >= pos / p.chunk * p.chunk);
             if (penalised && visible) s -= distance_penalty(r1, r2, pos - key);
             s = visible ? s : -INFINITY;
@@ -137,12 +159,15 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(const 
             }
         }
     }
+    }
     T* out = (T*)p.out;
 #pragma unroll
     for (int i = 0; i < PF_ROWS; ++i) {
         const int r = warp + i * PF_WARPS;
         if (r >= rows) continue;
-        const float inv = 1.f / l[i];
+        float factor = 1.f;
+        if (p.sink) with_sink(m[i], l[i], factor);
+        const float inv = factor / l[i];
 #pragma unroll
         for (int j = 0; j < DMAX / 32; ++j) {
             const int c = lane + 32 * j;
@@ -156,7 +181,7 @@ static int launch_prefill(const AttnParams& p, int max_q_len, cudaStream_t strea
     const size_t smem = ((size_t)PF_BQ * p.d + (size_t)PF_BK * (p.d + 1) + (size_t)PF_BK * p.dv + PF_BQ * PF_BK) * sizeof(float);
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(attention_prefill_kernel<T, DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+        cudaError_t err = cudaFuncSetAttribute(attention_prefill_kernel<T, DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (DMAX > 256 ? 200 : 100) * 1024);
         if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "attention_prefill: cannot raise shared memory: %s", cudaGetErrorString(err));
         configured = true;
     }
@@ -167,12 +192,14 @@ static int launch_prefill(const AttnParams& p, int max_q_len, cudaStream_t strea
 }
 
 static int check_common(const char* name, int n_seqs, int nq, int nkv, int d, int dv, const float* r1, const float* r2, int page_tokens,
-                        int ring_tokens, int window, int chunk, int nv) {
+                        int ring_tokens, int window, int chunk, int nv, int keep_first, int v_row) {
+    QT_REQUIRE(keep_first >= 0 && (keep_first == 0 || ring_tokens == 0), "%s: kept first keys (%d) do not go with a ring of %d tokens", name, keep_first, ring_tokens);
+    QT_REQUIRE(v_row >= dv, "%s: value rows of %d elements for values of %d", name, v_row, dv);
     QT_REQUIRE(chunk >= 0 && nv > 0 && nkv % nv == 0, "%s: chunk=%d, %d value heads for %d key heads", name, chunk, nv, nkv);
     QT_REQUIRE(n_seqs > 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "%s: bad head counts nq=%d nkv=%d (B=%d)", name, nq, nkv, n_seqs);
-    QT_REQUIRE(d > 0 && d <= 256, "%s: head_dim=%d is outside 1..256", name, d);
-    QT_REQUIRE(dv > 0 && dv <= 256, "%s: value head_dim=%d is outside 1..256", name, dv);
-    QT_REQUIRE((r1 == nullptr) == (r2 == nullptr), "%s: the distance penalty needs both of its factors", name);
+    QT_REQUIRE(d > 0 && d <= 640, "%s: head_dim=%d is outside 1..640", name, d);
+    QT_REQUIRE(dv > 0 && dv <= 512, "%s: value head_dim=%d is outside 1..512", name, dv);
+    QT_REQUIRE(r1 != nullptr || r2 == nullptr, "%s: the distance penalty needs its first factor", name);
     QT_REQUIRE(page_tokens > 0 && ring_tokens >= 0, "%s: bad cache geometry", name);
     QT_REQUIRE(ring_tokens == 0 || (window > 0 && ring_tokens >= window), "%s: a ring of %d tokens cannot hold a window of %d", name, ring_tokens, window);
     return QT_OK;
@@ -181,19 +208,22 @@ static int check_common(const char* name, int n_seqs, int nq, int nkv, int d, in
 extern "C" int qt_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
                                     const int* block_table, int max_blocks, const int* seq_start, const int* seq_past,
                                     int n_seqs, int max_q_len, int nq, int nkv, int d, int page_tokens, int ring_tokens,
-                                    int window, float scale, int dv, const float* r1, const float* r2, int chunk, int nv, void* stream) {
+                                    int window, float scale, int dv, const float* r1, const float* r2, int chunk, int nv,
+                                    int keep_first, int sink, int v_row, void* stream) {
     if (n_seqs == 0 || max_q_len == 0) return QT_OK;
     if (nv <= 0) nv = nkv;
-    int rc = check_common("attention_prefill", n_seqs, nq, nkv, d, dv, r1, r2, page_tokens, ring_tokens, window, chunk, nv);
+    if (v_row <= 0) v_row = dv;
+    int rc = check_common("attention_prefill", n_seqs, nq, nkv, d, dv, r1, r2, page_tokens, ring_tokens, window, chunk, nv, keep_first, v_row);
     if (rc) return rc;
     QT_REQUIRE(nq <= 65535 && n_seqs <= 65535, "attention_prefill: too many heads or sequences for one launch");
     AttnParams p{q, k_cache, v_cache, out, block_table, max_blocks, seq_start, seq_past, n_seqs, nq, nkv, d, page_tokens, ring_tokens, window, scale,
-                 dv, r1, r2, chunk, nv};
+                 dv, r1, r2, chunk, nv, keep_first, sink, v_row};
     cudaStream_t s = (cudaStream_t)stream;
     return QT_DISPATCH_DTYPE(dtype, "attention_prefill", {
         if (dv <= 64) return launch_prefill<T, 64>(p, max_q_len, s);
         if (dv <= 128) return launch_prefill<T, 128>(p, max_q_len, s);
-        return launch_prefill<T, 256>(p, max_q_len, s);
+        if (dv <= 256) return launch_prefill<T, 256>(p, max_q_len, s);
+        return launch_prefill<T, 512>(p, max_q_len, s);
     });
 }
 
@@ -235,10 +265,14 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
     int lo = p.window > 0 ? max(0, len - p.window) : 0;
     if (p.chunk > 0) lo = max(lo, (len - 1) / p.chunk * p.chunk);
     const int vh = kvh % p.nv;
-    const int span = len - lo;
+    // the visible keys are [0, keep_end) and [lo, len); the loops below walk them as one range of indices, of which
+    // index u stands for key u below keep_end and for key u + gap from there on
+    const int keep_end = (p.window > 0 && p.keep_first > 0) ? min(p.keep_first, lo) : 0;
+    const int gap = lo - keep_end;
+    const int span = len - gap;
     const int chunk = (span + dp.n_splits - 1) / dp.n_splits;
-    const int k_begin = lo + split * chunk;
-    const int k_end = min(len, k_begin + chunk);
+    const int k_begin = split * chunk;
+    const int k_end = min(span, k_begin + chunk);
     const int* table = p.block_table + (size_t)seq * p.max_blocks;
     const T* q = (const T*)p.q;
     const T* kc = (const T*)p.k_cache;
@@ -249,7 +283,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
 #pragma unroll
     for (int h = 0; h < DEC_HEADS; ++h) {
         r1[h] = penalised && h < nh ? p.r1[head_base + h] : 0.f;
-        r2[h] = penalised && h < nh ? p.r2[head_base + h] : 0.f;
+        r2[h] = penalised && h < nh ? (p.r2 ? p.r2[head_base + h] : -1.f) : 0.f;
     }
 
     for (int i = threadIdx.x; i < DEC_HEADS * d; i += blockDim.x) {
@@ -267,8 +301,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
     }
 
     for (int k0 = k_begin + warp * 32; k0 < k_end; k0 += DEC_WARPS * 32) {
-        const int key = k0 + lane;
-        const bool valid = key < k_end;
+        const bool valid = k0 + lane < k_end;
+        const int key = k0 + lane < keep_end ? k0 + lane : k0 + lane + gap;
         float s[DEC_HEADS];
 #pragma unroll
         for (int h = 0; h < DEC_HEADS; ++h) s[h] = 0.f;
@@ -298,7 +332,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
         }
         const int n_keys = min(32, k_end - k0);
         for (int kk = 0; kk < n_keys; ++kk) {
-            const T* vrow = vc + cache_offset(table, k0 + kk, p.ring_tokens, p.page_tokens, p.nv, vh, dv);
+            const T* vrow = vc + cache_offset(table, k0 + kk < keep_end ? k0 + kk : k0 + kk + gap, p.ring_tokens, p.page_tokens, p.nv, vh, p.v_row);
             float v[DMAX / 32];
 #pragma unroll
             for (int j = 0; j < DMAX / 32; ++j) {
@@ -338,7 +372,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
         }
         const int head = head_base + h;
         if (dp.n_splits == 1) {
-            ((T*)p.out)[((size_t)seq * p.nq + head) * dv + c] = from_float<T>(a_all / l_all);
+            float factor = 1.f;
+            if (p.sink) with_sink(m_all, l_all, factor);
+            ((T*)p.out)[((size_t)seq * p.nq + head) * dv + c] = from_float<T>(a_all * factor / l_all);
         } else {
             const size_t slot = ((size_t)seq * p.nq + head) * dp.n_splits + split;
             dp.part_acc[slot * dv + c] = a_all;
@@ -350,7 +386,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
 // One block per (sequence, head): out = sum_s acc_s e^{m_s - m} / sum_s l_s e^{m_s - m}; empty splits have m = -inf.
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                         T* __restrict__ out, int n_splits, int d) {
+                                         T* __restrict__ out, int n_splits, int d, int sink) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t item = blockIdx.x;   // seq * nq + head
@@ -361,13 +397,15 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc, con
         const float ms = part_ml[(item * n_splits + s) * 2];
         l_all += ms == -INFINITY ? 0.f : part_ml[(item * n_splits + s) * 2 + 1] * expf(ms - m_all);
     }
+    float factor = 1.f;
+    if (sink) with_sink(m_all, l_all, factor);
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float a = 0.f;
         for (int s = 0; s < n_splits; ++s) {
             const float ms = part_ml[(item * n_splits + s) * 2];
             if (ms != -INFINITY) a += part_acc[(item * n_splits + s) * d + c] * expf(ms - m_all);
         }
-        out[item * d + c] = from_float<T>(a / l_all);
+        out[item * d + c] = from_float<T>(a * factor / l_all);
     }
 }
 
@@ -377,7 +415,7 @@ static int launch_decode_heads(const DecodeParams& dp, cudaStream_t stream) {
     const size_t smem = ((size_t)DEC_HEADS * p.d + (size_t)DEC_WARPS * DEC_HEADS * p.dv + DEC_WARPS * DEC_HEADS * 2) * sizeof(float);
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(attention_decode_kernel<T, DMAX, DEC_HEADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+        cudaError_t err = cudaFuncSetAttribute(attention_decode_kernel<T, DMAX, DEC_HEADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (DMAX > 256 ? 100 : 64) * 1024);
         if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "attention_decode: cannot raise shared memory: %s", cudaGetErrorString(err));
         configured = true;
     }
@@ -386,7 +424,7 @@ static int launch_decode_heads(const DecodeParams& dp, cudaStream_t stream) {
     launch_kernel(attention_decode_kernel<T, DMAX, DEC_HEADS>, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, dp);
     QT_CHECK_LAUNCH("attention_decode");
     if (dp.n_splits > 1) {
-        launch_kernel(attention_combine_kernel<T>, dim3(p.n_seqs * p.nq), dim3(128), 0, stream, dp.part_acc, dp.part_ml, (T*)p.out, dp.n_splits, p.dv);
+        launch_kernel(attention_combine_kernel<T>, dim3(p.n_seqs * p.nq), dim3(128), 0, stream, dp.part_acc, dp.part_ml, (T*)p.out, dp.n_splits, p.dv, p.sink);
         QT_CHECK_LAUNCH("attention_combine");
     }
     return QT_OK;
@@ -397,7 +435,7 @@ static int launch_decode(const DecodeParams& dp, cudaStream_t stream) {
     const int group = dp.a.nq / dp.a.nkv;
     if (group == 1) return launch_decode_heads<T, DMAX, 1>(dp, stream);
     if (group == 2) return launch_decode_heads<T, DMAX, 2>(dp, stream);
-    if (group <= 4) return launch_decode_heads<T, DMAX, 4>(dp, stream);
+    if (group <= 4 || DMAX > 256) return launch_decode_heads<T, DMAX, 4>(dp, stream);      // the widest values: four heads' accumulators fill the registers
     return launch_decode_heads<T, DMAX, 8>(dp, stream);
 }
 
@@ -407,22 +445,24 @@ extern "C" int qt_attention_decode(const void* q, const void* k_cache, const voi
                                    const int* block_table, int max_blocks, const int* seq_len, int n_seqs, int nq,
                                    int nkv, int d, int page_tokens, int ring_tokens, int window, float scale,
                                    int n_splits, float* part_acc, float* part_ml, int dv, const float* r1, const float* r2,
-                                   int chunk, int nv, void* stream) {
+                                   int chunk, int nv, int keep_first, int sink, int v_row, void* stream) {
     if (n_seqs == 0) return QT_OK;
     if (nv <= 0) nv = nkv;
-    int rc = check_common("attention_decode", n_seqs, nq, nkv, d, dv, r1, r2, page_tokens, ring_tokens, window, chunk, nv);
+    if (v_row <= 0) v_row = dv;
+    int rc = check_common("attention_decode", n_seqs, nq, nkv, d, dv, r1, r2, page_tokens, ring_tokens, window, chunk, nv, keep_first, v_row);
     if (rc) return rc;
     QT_REQUIRE(n_splits >= 1 && n_splits <= 65535, "attention_decode: n_splits=%d", n_splits);
     QT_REQUIRE(n_splits == 1 || (part_acc && part_ml), "attention_decode: split results need scratch memory");
     QT_REQUIRE(n_seqs <= 65535, "attention_decode: too many sequences for one launch");
     DecodeParams dp{{q, k_cache, v_cache, out, block_table, max_blocks, nullptr, nullptr, n_seqs, nq, nkv, d, page_tokens, ring_tokens, window, scale,
-                     dv, r1, r2, chunk, nv},
+                     dv, r1, r2, chunk, nv, keep_first, sink, v_row},
                     seq_len, n_splits, part_acc, part_ml};
     cudaStream_t s = (cudaStream_t)stream;
     return QT_DISPATCH_DTYPE(dtype, "attention_decode", {
         if (dv <= 64) return launch_decode<T, 64>(dp, s);
         if (dv <= 128) return launch_decode<T, 128>(dp, s);
-        return launch_decode<T, 256>(dp, s);
+        if (dv <= 256) return launch_decode<T, 256>(dp, s);
+        return launch_decode<T, 512>(dp, s);
     });
 }
 

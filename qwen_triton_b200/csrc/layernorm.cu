@@ -1,0 +1,128 @@
+// Layer norm without bias around the float residual stream, and an activation on a product's sums.
+//
+// add_layernorm_kernel: one block per output row r, src = rows ? rows[r] : r.
+//   d = sum_s delta[s][src]                                   (float; split-K partial sums added in their order)
+//   if (post_weight) d = (d - mean(d)) / sqrt(var(d) + eps) * post_weight     (a norm on the sublayer's output)
+//   x = residual[src] + d;  if (!rows) residual[src] = x      (the stream is updated in place)
+//   out[r] = (x - mean(x)) / sqrt(var(x) + eps) * weight      (rounded once to the output type)
+// The variance is the mean of the squared deviations from the mean, taken in a second pass over the row, which the
+// block keeps in shared memory.  A layer that norms what a sublayer returns before adding it, and norms the stream
+// again for the next sublayer, is one launch per sublayer.
+//
+// activation_kernel: out = act(sum_s in[s]) elementwise, for a feed-forward of two matrices with no gate.
+#include "common.cuh"
+
+#include <math.h>
+
+using namespace qt;
+
+template <typename TD, typename TO>
+__global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_splits, size_t split_stride,
+                                     const float* __restrict__ post_weight, const float* __restrict__ weight, float eps,
+                                     TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float row[];            // [hidden]
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* res = residual + (size_t)src * hidden;
+    const float inv_n = 1.f / (float)hidden;
+    if (delta) {
+        float sum = 0.f;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float d = load_sum(delta, (size_t)src * hidden + i, n_splits, split_stride);
+            row[i] = d;
+            sum += d;
+        }
+        if (post_weight) {
+            const float mean = block_sum(sum, scratch) * inv_n;
+            float sq = 0.f;
+            for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+                const float c = row[i] - mean;
+                sq += c * c;
+            }
+            const float inv = rsqrtf(block_sum(sq, scratch) * inv_n + eps);
+            for (int i = threadIdx.x; i < hidden; i += blockDim.x) row[i] = (row[i] - mean) * inv * post_weight[i];
+        }
+    }
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float x = res[i] + (delta ? row[i] : 0.f);
+        row[i] = x;
+        if (!rows) res[i] = x;
+        sum += x;
+    }
+    const float mean = block_sum(sum, scratch) * inv_n;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float c = row[i] - mean;
+        sq += c * c;
+    }
+    const float inv = rsqrtf(block_sum(sq, scratch) * inv_n + eps);
+    TO* o = out + (size_t)r * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<TO>((row[i] - mean) * inv * weight[i]);
+}
+
+extern "C" int qt_add_layernorm(float* residual, const void* delta, int delta_dtype, int n_splits, long long split_stride,
+                                const float* post_weight, const float* weight, float eps, void* out, int out_dtype, const int* rows,
+                                int n_rows, int hidden, void* stream) {
+    QT_REQUIRE(n_rows >= 0 && hidden > 0 && n_splits >= 1, "add_layernorm: bad sizes rows=%d H=%d splits=%d", n_rows, hidden, n_splits);
+    QT_REQUIRE(eps > 0.f, "add_layernorm: eps must be positive");
+    QT_REQUIRE(delta || !post_weight, "add_layernorm: a norm on an addition that is not there");
+    if (n_rows == 0) return QT_OK;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    QT_REQUIRE(smem <= 200 * 1024, "add_layernorm: a row of %d elements does not fit shared memory", hidden);
+    cudaStream_t s = (cudaStream_t)stream;
+    int threads = ((hidden + 3) / 4 + 31) / 32 * 32;
+    threads = threads < 64 ? 64 : threads > 1024 ? 1024 : threads;
+#define QT_LAUNCH_LN(TD, TO)                                                                                                        \
+    do {                                                                                                                            \
+        if (smem > 48 * 1024) {                                                                                                     \
+            cudaError_t err = cudaFuncSetAttribute(add_layernorm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "add_layernorm: cannot raise shared memory: %s", cudaGetErrorString(err)); \
+        }                                                                                                                           \
+        launch_kernel(add_layernorm_kernel<TD, TO>, dim3(n_rows), dim3(threads), smem, s, residual, (const TD*)delta, n_splits,     \
+                      (size_t)split_stride, post_weight, weight, eps, (TO*)out, rows, hidden);                                      \
+    } while (0)
+    if (delta_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_LN(float, float);
+    else if (delta_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_LN(float, __nv_bfloat16);
+    else if (delta_dtype == QT_BF16 && out_dtype == QT_BF16) QT_LAUNCH_LN(__nv_bfloat16, __nv_bfloat16);
+    else if (delta_dtype == QT_BF16 && out_dtype == QT_F32) QT_LAUNCH_LN(__nv_bfloat16, float);
+    else QT_FAIL(QT_ERR_ARG, "add_layernorm: unknown element types %d/%d", delta_dtype, out_dtype);
+#undef QT_LAUNCH_LN
+    QT_CHECK_LAUNCH("add_layernorm");
+    return QT_OK;
+}
+
+// ----------------------------------------------------------------------------- activation on a product's sums
+template <typename TI, typename TO>
+__global__ void activation_kernel(const TI* __restrict__ in, int n_splits, size_t split_stride, TO* __restrict__ out, long long total, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+        out[i] = from_float<TO>(gate_activation<false>(load_sum(in, (size_t)i, n_splits, split_stride), act));
+}
+
+extern "C" int qt_activation(const void* in, int in_dtype, int n_splits, long long split_stride, void* out, int out_dtype, int n_rows,
+                             int cols, int act, void* stream) {
+    QT_REQUIRE(n_rows >= 0 && cols > 0 && n_splits >= 1, "activation: bad sizes rows=%d cols=%d splits=%d", n_rows, cols, n_splits);
+    QT_REQUIRE(act >= 0 && act < QT_ACT_COUNT, "activation: unknown activation code %d", act);
+    if (n_rows == 0) return QT_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long total = (long long)n_rows * cols;
+    long long blocks = (total + 255) / 256;
+    if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
+#define QT_LAUNCH_ACT(TI, TO) \
+    launch_kernel(activation_kernel<TI, TO>, dim3((unsigned)blocks), dim3(256), 0, s, (const TI*)in, n_splits, (size_t)split_stride, (TO*)out, total, act)
+    if (in_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_ACT(float, float);
+    else if (in_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_ACT(float, __nv_bfloat16);
+    else if (in_dtype == QT_BF16 && out_dtype == QT_BF16) QT_LAUNCH_ACT(__nv_bfloat16, __nv_bfloat16);
+    else if (in_dtype == QT_BF16 && out_dtype == QT_F32) QT_LAUNCH_ACT(__nv_bfloat16, float);
+    else QT_FAIL(QT_ERR_ARG, "activation: unknown element types %d/%d", in_dtype, out_dtype);
+#undef QT_LAUNCH_ACT
+    QT_CHECK_LAUNCH("activation");
+    return QT_OK;
+}
+
+QT_DEFINE_LAST_ERROR(layernorm)

@@ -48,9 +48,28 @@ _SIGNATURES = {
     },
     "attention": {
         "qt_attention_prefill": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int,
-                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_int, _c_int,
+                                 _c_int, _c_int, _c_int, _c_ptr],
         "qt_attention_decode": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int,
-                                _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+                                _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int,
+                                _c_int, _c_int, _c_int, _c_ptr],
+    },
+    "layernorm": {
+        "qt_add_layernorm": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_ptr],
+        "qt_activation": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    },
+    "short_conv": {
+        "qt_conv_qk_write": [_c_ptr, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,
+                             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+        "qt_gate_mul": [_c_ptr, _c_int, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    },
+    "latent": {
+        "qt_latent_prepare": [_c_ptr, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr,
+                              _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+        "qt_latent_query_rot": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                _c_int, _c_ptr],
+        "qt_head_product": [_c_ptr, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ll, _c_ll, _c_int,
+                            _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     },
     "experts": {
         "qt_experts_by_pair": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -379,6 +398,148 @@ def map_difference(ctx: torch.Tensor, out: torch.Tensor, lam: float, eps: float,
           float(post), _stream())
 
 
+def add_layernorm(residual: torch.Tensor, delta: GemmOut | None, post_weight: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                  out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
+    """Layer norm without bias around the float stream: d = delta, normed with ``post_weight`` first where that is given;
+    stream += d; out = (stream - mean) / sqrt(var + eps) * weight, the variance being the mean squared deviation.
+
+    Without ``rows`` every row of ``residual`` [T, H] is updated in place and normed into ``out`` [T, H]; with ``rows``
+    (int32 [K]) only those rows are normed into ``out`` [K, H] and the stream is left as it is."""
+    hidden = residual.shape[1]
+    _need(residual, "residual", torch.float32)
+    _need(weight, "weight", torch.float32, (hidden,))
+    if post_weight is not None:
+        _need(post_weight, "post_weight", torch.float32, (hidden,))
+    n_rows = residual.shape[0] if rows is None else rows.shape[0]
+    _need(out, "out", shape=(n_rows, hidden))
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    if delta is not None and (not delta.tensor.is_cuda or (delta.rows, delta.cols) != tuple(residual.shape)):
+        raise KernelError(f"add_layernorm: delta {tuple(delta.tensor.shape)} does not match the stream {tuple(residual.shape)}")
+    _call("layernorm", "qt_add_layernorm", _ptr(residual), _ptr(delta.tensor) if delta else None,
+          _code(delta.tensor, "delta") if delta else F32, delta.n_splits if delta else 1, delta.split_stride if delta else 0,
+          _ptr(post_weight), _ptr(weight), float(eps), _ptr(out), _code(out, "out"), _ptr(rows), n_rows, hidden, _stream())
+
+
+def activation(x: GemmOut, out: torch.Tensor, name: str = "gelu") -> None:
+    """out [T, N] = act(x) elementwise in float, x a product's sums; ``name`` is one of ``ACTIVATIONS``."""
+    _need(out, "out", shape=(x.rows, x.cols))
+    _call("layernorm", "qt_activation", _ptr(x.tensor), _code(x.tensor, "x"), x.n_splits, x.split_stride, _ptr(out), _code(out, "out"),
+          x.rows, x.cols, activation_code(name), _stream())
+
+
+def conv_qk_write(proj: GemmOut, taps: torch.Tensor, kept: torch.Tensor, ctx, q_out: torch.Tensor, k_cache: torch.Tensor | None,
+                  block_table: torch.Tensor | None, num_heads: int, num_kv_heads: int, head_dim: int, page_tokens: int,
+                  ring_tokens: int, write_kv: bool = True) -> None:
+    """A short causal convolution over time on every channel of the queries and keys that lead the columns of ``proj``
+    (float sums [*, T, >= (nq + nkv) d]), in float: ``taps`` [channels, n] with the last column the current token's; the
+    inputs before a step's first token come from ``kept`` [slots + 1, n - 1, channels], zeros at a sequence's start,
+    which is then brought up to date.  Queries go to ``q_out`` [T, nq, d], keys into the paged cache."""
+    tokens = proj.rows
+    channels = (num_heads + num_kv_heads) * head_dim
+    n_taps = taps.shape[1]
+    _need(proj.tensor, "proj", torch.float32)
+    _need(taps, "taps", torch.float32, (channels, n_taps))
+    _need(kept, "kept", torch.float32)
+    if tuple(kept.shape[1:]) != (max(n_taps - 1, 1), channels):
+        raise KernelError(f"conv_qk_write: kept inputs {tuple(kept.shape)} are not [slots, {max(n_taps - 1, 1)}, {channels}]")
+    _need(q_out, "q_out", shape=(tokens, num_heads, head_dim))
+    max_blocks = 0
+    if write_kv:
+        _need(block_table, "block_table", torch.int32)
+        max_blocks = block_table.shape[1]
+        _need(k_cache, "k_cache", q_out.dtype)
+        if tuple(k_cache.shape[1:]) != (num_kv_heads, page_tokens, head_dim):
+            raise KernelError(f"k_cache: shape {tuple(k_cache.shape)} is not [pages, {num_kv_heads}, {page_tokens}, {head_dim}]")
+    _call("short_conv", "qt_conv_qk_write", _ptr(proj.tensor), proj.n_splits, proj.split_stride, proj.cols, _ptr(taps), _ptr(kept),
+          _ptr(ctx.token_seq), _ptr(ctx.token_pos), _ptr(ctx.seq_start), _ptr(ctx.slots), _ptr(q_out), _ptr(k_cache), _code(q_out, "q_out"),
+          _ptr(block_table), max_blocks, tokens, ctx.n_seqs, num_heads, num_kv_heads, head_dim, n_taps, page_tokens, ring_tokens,
+          1 if write_kv else 0, _stream(), launches=2 if n_taps > 1 else 1)
+
+
+def gate_mul(x: torch.Tensor, gate: GemmOut, offset: int) -> None:
+    """x [T, N] *= sigmoid(columns ``offset`` .. ``offset + N`` of ``gate``), in float, in place."""
+    _need(x, "x")
+    _need(gate.tensor, "gate", torch.float32)
+    if x.dim() != 2 or gate.rows != x.shape[0]:
+        raise KernelError(f"gate_mul: x {tuple(x.shape)} and a gate of {gate.rows} rows")
+    _call("short_conv", "qt_gate_mul", _ptr(x), _code(x, "x"), _ptr(gate.tensor), gate.n_splits, gate.split_stride, gate.cols, int(offset),
+          x.shape[0], x.shape[1], _stream())
+
+
+def latent_prepare(proj: GemmOut, q_norm: torch.Tensor, kv_norm: torch.Tensor | None, eps: float, cos_sin: torch.Tensor | None,
+                   cq_out: torch.Tensor, cache: torch.Tensor | None, token_seq: torch.Tensor, token_pos: torch.Tensor,
+                   block_table: torch.Tensor | None, rank: int, rot: int, page_tokens: int, ring_tokens: int, write_kv: bool = True) -> None:
+    """From the float sums ``proj`` [*, T, >= q_rank (+ rank + rot)] of a latent-attention mixer's first projection: the
+    query latent's RMS norm (``q_norm`` [q_rank]) into ``cq_out`` [T, q_rank] and, with ``write_kv``, the cache row of every
+    token: the key/value latent's RMS norm (``kv_norm`` [rank]) followed by the shared key part of ``rot`` elements, of
+    which the first ``cos_sin.shape[1]`` are rotated by the token's position.  ``cache`` is [pages, 1, page_tokens, rank + rot]."""
+    tokens = proj.rows
+    q_rank = q_norm.shape[0]
+    _need(proj.tensor, "proj", torch.float32)
+    _need(q_norm, "q_norm", torch.float32)
+    _need(cq_out, "cq_out", shape=(tokens, q_rank))
+    _need(token_seq, "token_seq", torch.int32, (tokens,))
+    _need(token_pos, "token_pos", torch.int32, (tokens,))
+    rotary_dim, max_pos, max_blocks = 0, 0, 0
+    if cos_sin is not None:
+        _need(cos_sin, "cos_sin", torch.float32)
+        max_pos, rotary_dim = cos_sin.shape
+    if write_kv:
+        _need(kv_norm, "kv_norm", torch.float32, (rank,))
+        _need(block_table, "block_table", torch.int32)
+        max_blocks = block_table.shape[1]
+        _need(cache, "cache", cq_out.dtype)
+        if tuple(cache.shape[1:]) != (1, page_tokens, rank + rot):
+            raise KernelError(f"cache: shape {tuple(cache.shape)} is not [pages, 1, {page_tokens}, {rank + rot}]")
+    _call("latent", "qt_latent_prepare", _ptr(proj.tensor), proj.n_splits, proj.split_stride, proj.cols, _ptr(q_norm), _ptr(kv_norm),
+          float(eps), _ptr(cos_sin), rotary_dim, max_pos, _ptr(cq_out), _ptr(cache), _code(cq_out, "cq_out"), _ptr(token_seq),
+          _ptr(token_pos), _ptr(block_table), max_blocks, tokens, q_rank, int(rank), int(rot), page_tokens, ring_tokens,
+          1 if write_kv else 0, _stream())
+
+
+def latent_query_rot(q: GemmOut, cos_sin: torch.Tensor | None, token_pos: torch.Tensor, out: torch.Tensor, heads: int, dim: int, rot: int,
+                     out_offset: int) -> None:
+    """The last ``rot`` elements of every head of ``q`` [*, T, heads (dim + rot)], the first ``cos_sin.shape[1]`` of them
+    rotated by the token's position, into ``out`` [T, heads, row] at ``out_offset`` of every head's row."""
+    tokens = q.rows
+    if q.cols != heads * (dim + rot) or out.dim() != 3 or tuple(out.shape[:2]) != (tokens, heads):
+        raise KernelError(f"latent_query_rot: q {tuple(q.tensor.shape)}, out {tuple(out.shape)} for {heads} heads of {dim} + {rot}")
+    _need(out, "out")
+    _need(token_pos, "token_pos", torch.int32, (tokens,))
+    rotary_dim = 0
+    if cos_sin is not None:
+        _need(cos_sin, "cos_sin", torch.float32)
+        rotary_dim = cos_sin.shape[1]
+    _call("latent", "qt_latent_query_rot", _ptr(q.tensor), _code(q.tensor, "q"), q.n_splits, q.split_stride, _ptr(cos_sin), rotary_dim,
+          _ptr(token_pos), _ptr(out), _code(out, "out"), tokens, heads, dim, rot, out.shape[2], int(out_offset), _stream())
+
+
+def head_product(x, weight: torch.Tensor, out: torch.Tensor, *, x_row: int, x_head: int, x_offset: int = 0, out_offset: int = 0,
+                 gate: GemmOut | None = None, gate_offset: int = 0) -> None:
+    """A product per head: out[t, h, out_offset + n] = sum_k x[t, h, k] weight[h, n, k], every head with a matrix of its own,
+    summed in float.  ``x`` is a tensor or a ``GemmOut`` (partial sums are added first) whose element (t, h, k) lies at
+    t * x_row + h * x_head + x_offset + k; ``out`` is [T, heads, row].  With ``gate`` (float sums [*, T, cols]) the result
+    is multiplied by sigmoid(gate[t, gate_offset + h * N + n])."""
+    heads, n, k = weight.shape
+    _need(weight, "weight")
+    _need(out, "out")
+    tokens = out.shape[0]
+    if out.dim() != 3 or out.shape[1] != heads or out_offset + n > out.shape[2]:
+        raise KernelError(f"head_product: out {tuple(out.shape)} for {heads} heads of {n} at {out_offset}")
+    if isinstance(x, GemmOut):
+        x_tensor, splits, stride = x.tensor, x.n_splits, x.split_stride
+    else:
+        _need(x, "x")
+        x_tensor, splits, stride = x, 1, 0
+    if gate is not None:
+        _need(gate.tensor, "gate", torch.float32)
+    _call("latent", "qt_head_product", _ptr(x_tensor), _code(x_tensor, "x"), splits, stride, int(x_row), int(x_head), int(x_offset),
+          _ptr(weight), _code(weight, "weight"), _ptr(out), _code(out, "out"), out.shape[1] * out.shape[2], out.shape[2], int(out_offset),
+          _ptr(gate.tensor) if gate is not None else None, gate.n_splits if gate is not None else 1,
+          gate.split_stride if gate is not None else 0, gate.cols if gate is not None else 0, int(gate_offset), tokens, heads, n, k, _stream())
+
+
 # ----------------------------------------------------------------------------- the gated delta rule
 def delta_prepare(proj: GemmOut, taps: torch.Tensor, kept: torch.Tensor, ctx, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                   beta: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int, unit_eps: float) -> None:
@@ -522,12 +683,14 @@ def swiglu(gate_up: GemmOut, out: torch.Tensor, group: int = 0, activation: str 
 
 
 # ----------------------------------------------------------------------------- attention
-def _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty=None):
+def _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty=None, v_dim=None):
     _need(q, "q")
     tokens, num_heads, head_dim = q.shape
     _need(k_cache, "k_cache", q.dtype)
     _need(v_cache, "v_cache", q.dtype)
-    v_dim = v_cache.shape[-1]                       # values may have a head size of their own
+    if v_dim is not None and not 0 < v_dim <= v_cache.shape[-1]:
+        raise KernelError(f"values of {v_dim} elements in cache rows of {v_cache.shape[-1]}")
+    v_dim = v_dim or v_cache.shape[-1]              # values may have a head size of their own, or be the head of longer rows
     _need(out, "out", q.dtype, (tokens, num_heads, v_dim))
     if tuple(k_cache.shape[1:]) != (num_kv_heads, page_tokens, head_dim):
         raise KernelError(f"cache shape {tuple(k_cache.shape)} is not [pages, {num_kv_heads}, {page_tokens}, {head_dim}]")
@@ -536,8 +699,18 @@ def _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_t
     _need(block_table, "block_table", torch.int32)
     if penalty is not None:
         for name, factor in zip(("r1", "r2"), penalty):
-            _need(factor, f"distance penalty {name}", torch.float32, (num_heads,))
+            if factor is not None or name == "r1":
+                _need(factor, f"distance penalty {name}", torch.float32, (num_heads,))
     return tokens, num_heads, head_dim
+
+
+def _generic_only(penalty, keep_first: int, sink: bool, v_dim, impl: str | None) -> bool:
+    """Whether a call asks for what only the generic attention kernels compute: a linear distance penalty (``penalty`` =
+    (slopes, None)), kept first keys, a softmax sink, or values that are the head of the cached key rows."""
+    special = (penalty is not None and penalty[1] is None) or keep_first > 0 or sink or v_dim is not None
+    if special and impl not in (None, "generic"):
+        raise KernelError(f"attention kernel {impl!r} takes no linear penalty, kept first keys, sink or values inside the key rows")
+    return special
 
 
 def _plain_attention(q: torch.Tensor, v_cache: torch.Tensor, penalty) -> bool:
@@ -596,15 +769,20 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
                       block_table: torch.Tensor, seq_start: torch.Tensor, seq_past: torch.Tensor, max_q_len: int,
                       num_kv_heads: int, page_tokens: int, ring_tokens: int, window: int | None, scale: float,
                       impl: str | None = None, penalty: tuple[torch.Tensor, torch.Tensor] | None = None,
-                      chunk: int | None = None) -> None:
+                      chunk: int | None = None, keep_first: int = 0, sink: bool = False, v_dim: int | None = None) -> None:
     """Causal attention of packed sequences over the cache (which already holds this step's keys).
     ``chunk``: a query at position i sees key j only if i // chunk == j // chunk as well.  A value cache with fewer
     heads than the key cache serves key head g with value head g % (value heads).
     ``impl`` forces a kernel ("tc": tcgen05, "mma": mma.sync, "generic"); by default the shape decides.
     ``penalty`` = (r1, r2), float [heads] each: the score of key j for the query at position i loses
-    r1_h * ln(1 + r2_h * (i - j))."""
-    _, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty)
-    if not _plain_attention(q, v_cache, penalty):
+    r1_h * ln(1 + r2_h * (i - j)); ``penalty`` = (slopes, None): it loses slope_h * (i - j).
+    ``keep_first``: a windowed query also sees the keys at positions below it.  ``sink``: the softmax has one more term
+    of score 0 without a value.  ``v_dim``: the values are the first ``v_dim`` elements of the rows of ``v_cache`` (which
+    may be the key cache itself)."""
+    _, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty, v_dim)
+    if _generic_only(penalty, keep_first, sink, v_dim, impl):
+        impl = "generic"
+    elif not _plain_attention(q, v_cache, penalty):
         impl = _penalised_choice(q, v_cache, page_tokens, scale, impl, "mma")
     n_seqs = seq_past.shape[0]
     _need(seq_start, "seq_start", torch.int32, (n_seqs + 1,))
@@ -627,8 +805,9 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         return
     _call("attention", "qt_attention_prefill", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q, "q"),
           _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, int(max_q_len), num_heads,
-          num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale), v_cache.shape[-1],
-          _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, int(chunk or 0), v_cache.shape[1], _stream())
+          num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale), int(v_dim or v_cache.shape[-1]),
+          _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, int(chunk or 0), v_cache.shape[1],
+          int(keep_first), 1 if sink else 0, v_cache.shape[-1], _stream())
 
 
 def _ws_merges_in_cluster(n_splits: int, warps: int, group: int, head_dim: int) -> bool:
@@ -647,7 +826,8 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      block_table: torch.Tensor, seq_len: torch.Tensor, num_kv_heads: int, page_tokens: int,
                      ring_tokens: int, window: int | None, scale: float, n_splits: int,
                      part_acc: torch.Tensor | None, part_ml: torch.Tensor | None, impl: str | None = None,
-                     warps: int = 1, penalty: tuple[torch.Tensor, torch.Tensor] | None = None, chunk: int | None = None) -> None:
+                     warps: int = 1, penalty: tuple[torch.Tensor, torch.Tensor] | None = None, chunk: int | None = None,
+                     keep_first: int = 0, sink: bool = False, v_dim: int | None = None) -> None:
     """One query token per sequence; ``seq_len`` counts the keys it sees (its own included).
 
     With ``n_splits`` > 1 the keys of each sequence are cut into that many ranges whose partial
@@ -656,16 +836,18 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     ranges, n_splits partial results; the default where it applies) and "mma" (the four warps of a block
     share each tile); "generic" takes every element type and head size.
     """
-    n_seqs, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty)
+    n_seqs, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty, v_dim)
     _need(seq_len, "seq_len", torch.int32, (n_seqs,))
     if impl == "mma" and _special_mask(k_cache, v_cache, chunk):
         raise KernelError("the block-tile decode kernel takes no mask in chunks and no value heads shared by several key heads")
-    if not _plain_attention(q, v_cache, penalty):
+    if _generic_only(penalty, keep_first, sink, v_dim, impl):
+        impl = "generic"
+    elif not _plain_attention(q, v_cache, penalty):
         impl = _penalised_choice(q, v_cache, page_tokens, scale, impl, "ws")
     if n_splits > 1:
         _need(part_acc, "part_acc", torch.float32)
         _need(part_ml, "part_ml", torch.float32)
-        if part_acc.numel() < n_seqs * num_heads * n_splits * v_cache.shape[-1] or part_ml.numel() < n_seqs * num_heads * n_splits * 2:
+        if part_acc.numel() < n_seqs * num_heads * n_splits * (v_dim or v_cache.shape[-1]) or part_ml.numel() < n_seqs * num_heads * n_splits * 2:
             raise KernelError("attention_decode: scratch is too small for this batch and split count")
     if impl == "ws" and not attention_mma_supported(q, page_tokens):
         raise KernelError(f"the tensor-core attention kernels do not take {q.dtype}, head_dim={q.shape[2]}, pages of {page_tokens}")
@@ -685,8 +867,8 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         _call("attention_mma", "qt_attention_decode_mma", *common, _ptr(part_acc), _ptr(part_ml), _stream(), launches=launches)
     else:
         _call("attention", "qt_attention_decode", *common[:4], _code(q, "q"), *common[4:], _ptr(part_acc), _ptr(part_ml),
-              v_cache.shape[-1], _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None,
-              int(chunk or 0), v_cache.shape[1], _stream(), launches=launches)
+              int(v_dim or v_cache.shape[-1]), _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None,
+              int(chunk or 0), v_cache.shape[1], int(keep_first), 1 if sink else 0, v_cache.shape[-1], _stream(), launches=launches)
 
 
 # ----------------------------------------------------------------------------- experts chosen by a table

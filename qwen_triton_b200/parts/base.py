@@ -72,13 +72,15 @@ def part_class(family: str, spec: PartSpec) -> type:
 class KVRequest:
     """Keys and values per token: all of them (``window`` None) or the last ``window``.  Values have the keys' head
     size unless ``v_head_dim`` gives their own, and as many heads as the keys unless ``v_heads`` says otherwise
-    (several key heads, one per score map, over one set of values)."""
+    (several key heads, one per score map, over one set of values).  With ``shared_values`` nothing is stored for
+    the values: they are the cached keys, or the leading elements of them, and the view's ``v`` is its ``k``."""
 
     kv_heads: int
     head_dim: int
     window: int | None = None
     v_head_dim: int | None = None
     v_heads: int | None = None
+    shared_values: bool = False
 
 
 @dataclass(frozen=True)
@@ -190,6 +192,7 @@ class ResidualStream:
         self.residual = residual
         self._pending: GemmOut | DeferredProduct | None = None
         self.more: list[GemmOut] = []      # further additions beside ``pending`` (a block whose parts run side by side)
+        self.post = None                   # a norm that the pending addition passes before it is added (``add(..., post=)``)
 
     @property
     def pending(self) -> GemmOut | None:
@@ -201,10 +204,13 @@ class ResidualStream:
     def pending(self, value: GemmOut | None) -> None:
         self._pending = value
 
-    def add(self, delta: "GemmOut | DeferredProduct") -> None:
+    def add(self, delta: "GemmOut | DeferredProduct", post=None) -> None:
+        """Leave ``delta`` pending.  With ``post`` (a norm part) the addition is to be normed by it first: only a norm
+        that says ``folds_post_norm`` takes such a stream (it reads ``stream.post`` and clears it); the others refuse it."""
         if self._pending is not None:
             raise RuntimeError("the residual stream already has a pending addition; apply a norm first")
         self._pending = delta
+        self.post = post
 
     def add_beside(self, delta: GemmOut) -> None:
         """One more addition beside the pending one, for arrangements whose parts all read the same normed rows.  Only a

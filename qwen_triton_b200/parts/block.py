@@ -87,6 +87,59 @@ class PreNormBlock:
         stream.add(self.feed_forward.forward(x, ctx))
 
 
+@register_block("sandwich")
+class SandwichBlock(PreNormBlock):
+    """A norm before and after each sublayer: h += post1(mixer(norm1(h))); h += post2(feed_forward(norm2(h))).
+
+    What a sublayer returns is left pending on the stream together with the norm it is to pass (``stream.add(...,
+    post=)``); the next norm in front of a sublayer (or the model's final norm) folds both, so it must be one that says
+    ``folds_post_norm``.  The tensors of the two further norms are named by the block parameters ``mixer_post_norm`` and
+    ``feed_forward_post_norm``."""
+
+    def __init__(self, layer: LayerSpec, runtime: Runtime) -> None:
+        super().__init__(layer, runtime)
+        names = self._post_names(layer)
+        norm = layer.extra.get("post_norm", layer.norm)
+        self.mixer_post_norm = part_class("norm", norm)(norm.params, names[0], runtime)
+        self.feed_forward_post_norm = None
+        if layer.feed_forward is not None:
+            self.feed_forward_post_norm = part_class("norm", norm)(norm.params, names[1], runtime)
+        for part in (self.mixer_norm, self.feed_forward_norm):
+            if part is not None and not getattr(part, "folds_post_norm", False):
+                raise ValueError(f"{layer.prefix}: a sandwich block needs norms that fold an addition's own norm")
+
+    @staticmethod
+    def _post_names(layer: LayerSpec) -> tuple[str, str]:
+        p = layer.block.params
+        return (f"{layer.prefix}.{p.get('mixer_post_norm', 'mixer_post_norm')}",
+                f"{layer.prefix}.{p.get('feed_forward_post_norm', 'feed_forward_post_norm')}")
+
+    @classmethod
+    def expected_tensors(cls, layer: LayerSpec) -> dict[str, TensorSpec]:
+        out = super().expected_tensors(layer)
+        names = cls._post_names(layer)
+        norm = layer.extra.get("post_norm", layer.norm)
+        out.update(part_class("norm", norm).expected_tensors(norm.params, names[0]))
+        second = part_class("norm", norm).expected_tensors(norm.params, names[1])
+        if layer.feed_forward is None:
+            second = {name: replace(spec, optional=True) for name, spec in second.items()}
+        out.update(second)
+        return out
+
+    def parts(self) -> tuple:
+        return super().parts() + tuple(part for part in (self.mixer_post_norm, self.feed_forward_post_norm) if part is not None)
+
+    def forward(self, stream: ResidualStream, ctx, cache) -> None:
+        x = self.mixer_norm.apply(stream)
+        result = self.mixer.forward(x, ctx, cache)
+        stream.add(result.run() if isinstance(result, DeferredProduct) else result, post=self.mixer_post_norm)
+        if self.feed_forward is None:
+            return
+        x = self.feed_forward_norm.apply(stream)
+        result = self.feed_forward.forward(x, ctx)
+        stream.add(result.run() if isinstance(result, DeferredProduct) else result, post=self.feed_forward_post_norm)
+
+
 @register_block("parallel")
 class ParallelBlock(PreNormBlock):
     """One norm, read by the mixer and by the feed-forward alike: h = norm(x); x += mixer(h) + feed_forward(h).

@@ -90,6 +90,57 @@ class GatedMLP:
         return DeferredProduct(self.down, act) if self.down.fusable(tokens) else self.down(act)
 
 
+@register_feed_forward("plain_mlp")
+class PlainMLP:
+    """A feed-forward of two matrices with an activation between them and no gate: down(act(up(x))).
+
+    Parameters: ``hidden_size``, ``intermediate_size``, ``activation`` (one of ``kernels.ACTIVATIONS``, default the exact
+    GELU), the tensor-name pieces ``up``, ``down``, ``weight_suffix`` (default ".weight"), ``float_out`` (the down
+    projection hands on float sums) and ``buffers``.  The activation is taken on the up product's sums in float."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix: str, runtime: Runtime) -> None:
+        self.prefix = prefix
+        self.runtime = runtime
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.activation = params.get("activation", "gelu")
+        if self.activation not in kernels.ACTIVATIONS:
+            raise ValueError(f"{prefix}: activation {self.activation!r} is not one of {sorted(kernels.ACTIVATIONS)}")
+        self.names = self._names(params)
+        float_out = bool(params.get("float_out", False))
+        key = str(params.get("buffers", "mlp"))
+        self.up = Linear(f"{key}.up.plain", self.inter, self.hidden, runtime)
+        self.down = Linear(f"{key}.down" + (".float" if float_out else ""), self.hidden, self.inter, runtime, float_out=float_out)
+        self.act_buffer = f"{key}.act"
+        runtime.workspace.declare(self.act_buffer, runtime.max_step_tokens * self.inter, runtime.dtype)
+
+    @staticmethod
+    def _names(params) -> dict[str, str]:
+        suffix = str(params.get("weight_suffix", ".weight"))
+        return {k: params.get(k, f"{k}_proj") + suffix for k in ("up", "down")}
+
+    @classmethod
+    def expected_tensors(cls, params, prefix: str) -> dict[str, TensorSpec]:
+        hidden, inter = int(params["hidden_size"]), int(params["intermediate_size"])
+        n = cls._names(params)
+        std = float(params.get("init_std", 0.02))
+        return {f"{prefix}.{n['up']}": TensorSpec((inter, hidden), init_std=std),
+                f"{prefix}.{n['down']}": TensorSpec((hidden, inter), init_std=std)}
+
+    def load(self, source) -> None:
+        n, p = self.names, self.prefix
+        self.up.set_weight(source(f"{p}.{n['up']}"))
+        self.down.set_weight(source(f"{p}.{n['down']}"))
+
+    def forward(self, x, ctx):
+        tokens = x.shape[0]
+        act = self.runtime.workspace.view(self.act_buffer, tokens, self.inter)
+        kernels.activation(self.up(x), act, self.activation)
+        return self.down(act)
+
+
 # Most (token, expert) pairs that run as matrix-vector passes, each streaming its expert's rows once: up to two pairs
 # per expert, and never more than 64.  Beyond, pairs that share an expert would each read its weights again (from L2 at
 # best), so the pairs are ordered by expert and the products run in tiles on the tensor cores, every expert read once

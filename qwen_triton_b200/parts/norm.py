@@ -57,6 +57,8 @@ class RMSNorm:
         ws = self.runtime.workspace
         if stream.more:
             raise RuntimeError(f"{self.name}: this norm folds one pending addition; the stream holds {1 + len(stream.more)}")
+        if stream.post is not None:
+            raise RuntimeError(f"{self.name}: the pending addition is to pass a norm of its own first, which this norm does not fold")
         deferred = stream.take_deferred()
         if deferred is not None:
             count = stream.residual.shape[0]
@@ -117,6 +119,8 @@ class DynamicTanh:
         self.alpha = float(source(alpha).float().reshape(-1)[0])          # read once, when the model is loaded
 
     def apply(self, stream: ResidualStream, rows: torch.Tensor | None = None, lazy: bool = False):
+        if stream.post is not None:
+            raise RuntimeError(f"{self.name}: the pending addition is to pass a norm of its own first, which this norm does not fold")
         deltas = stream.take_all() if rows is None else ([stream.pending] if stream.pending is not None else []) + stream.more
         count = stream.residual.shape[0] if rows is None else rows.shape[0]
         out = self.runtime.workspace.view("normed", count, self.size)
@@ -127,4 +131,55 @@ class DynamicTanh:
                 raise RuntimeError(f"{self.name}: more than two pending additions while only listed rows are wanted")
             deltas = deltas[2:]
         kernels.add_dyt(stream.residual, deltas, self.weight, self.bias, self.alpha, out, rows)
+        return out
+
+
+@register_norm("layernorm")
+class LayerNorm:
+    """y = (x - mean) / sqrt(var + eps) * w over the row, the variance being the mean of the squared deviations; a weight
+    and no bias.  Parameters: ``size``, ``eps``, ``suffix`` (what the weight's tensor name adds to the norm's name,
+    default ".weight") and ``scale`` (default 1): a constant that multiplies the weight when it is loaded, for a model
+    whose logits are the head's product times a constant (the product is linear, so the factor may ride on its input).
+
+    ``folds_post_norm``: where the stream's pending addition is to pass a norm of its own first (``stream.post``, another
+    norm of this kind: a layer that norms what a sublayer returns before adding it), the same launch norms the addition,
+    adds it and norms the new stream."""
+
+    graph_safe = True
+    offers_scaled_rows = False
+    folds_post_norm = True
+
+    def __init__(self, params, name: str, runtime: Runtime) -> None:
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+        self.scale = float(params.get("scale", 1.0))
+        self.tensor = name + str(params.get("suffix", ".weight"))
+        self.name = name
+        self.runtime = runtime
+        self.weight: torch.Tensor | None = None
+        runtime.workspace.declare("normed", runtime.max_step_tokens * self.size, runtime.dtype)
+
+    @classmethod
+    def expected_tensors(cls, params, name: str) -> dict[str, TensorSpec]:
+        return {name + str(params.get("suffix", ".weight")): TensorSpec((int(params["size"]),), role="vector", init_std=0.1, init_mean=1.0)}
+
+    def load(self, source) -> None:
+        self.weight = to_device(source(self.tensor), torch.float32, self.runtime.device)
+        if self.scale != 1.0:
+            self.weight = self.weight * self.scale
+
+    def apply(self, stream: ResidualStream, rows: torch.Tensor | None = None, lazy: bool = False):
+        if stream.more:
+            raise RuntimeError(f"{self.name}: this norm folds one pending addition; the stream holds {1 + len(stream.more)}")
+        post = stream.post
+        if post is not None and not isinstance(post, LayerNorm):
+            raise RuntimeError(f"{self.name}: the pending addition's own norm is not a layer norm")
+        if post is not None and post.eps != self.eps:
+            raise RuntimeError(f"{self.name}: the pending addition's own norm has eps={post.eps}, this one {self.eps}")
+        count = stream.residual.shape[0] if rows is None else rows.shape[0]
+        out = self.runtime.workspace.view("normed", count, self.size)
+        kernels.add_layernorm(stream.residual, stream.pending, post.weight if post is not None else None, self.weight, self.eps, out, rows)
+        if rows is None:
+            stream.pending = None
+            stream.post = None
         return out

@@ -44,6 +44,49 @@ class RotaryTable:
         return torch.cat((angles.cos(), angles.sin()), dim=-1).to(torch.float32).contiguous().to(self.runtime.device)
 
 
+@register_position("rope_yarn")
+class YarnRotaryTable:
+    """Rotary angles whose slow pairs are stretched (YaRN): with f_i = theta^(-2i/rd) and, for a pair that turns t times
+    within ``original`` positions, where(t) = rd ln(original / (2 pi t)) / (2 ln theta), the pairs below lo =
+    max(floor(where(fast)), 0) keep f_i, those above hi = min(ceil(where(slow)), rd - 1) turn at f_i / factor, and those
+    between blend the two by ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1).  cos and sin are multiplied by
+    ``magnitude`` (default 0.1 ln(factor) + 1).  Frequencies and angles are formed in float64, cos and sin rounded once
+    to float.  Parameters: ``theta``, ``rotary_dim``, ``head_dim``, ``factor``, ``original``, ``fast``, ``slow``."""
+
+    interleaved = False
+
+    def __init__(self, params, runtime: Runtime) -> None:
+        import math
+        self.theta = float(params["theta"])
+        self.rotary_dim = int(params["rotary_dim"])
+        if self.rotary_dim % 2 or self.rotary_dim <= 0 or self.rotary_dim > int(params["head_dim"]):
+            raise ValueError(f"rotary_dim={self.rotary_dim} must be even and within head_dim={params['head_dim']}")
+        self.factor, self.original = float(params["factor"]), float(params["original"])
+        self.fast, self.slow = float(params["fast"]), float(params["slow"])
+        if self.factor <= 0 or self.original <= 0 or self.fast <= 0 or self.slow <= 0 or self.theta <= 1:
+            raise ValueError("YaRN scaling needs positive factor, original, fast and slow, and theta above 1")
+        self.magnitude = float(params["magnitude"]) if params.get("magnitude") is not None else 0.1 * math.log(self.factor) + 1.0
+        self.runtime = runtime
+
+    def key(self) -> tuple:
+        return ("rope_yarn", self.theta, self.rotary_dim, self.factor, self.original, self.fast, self.slow, self.magnitude)
+
+    def frequencies(self) -> torch.Tensor:
+        import math
+        half = self.rotary_dim // 2
+        plain = self.theta ** (-torch.arange(half, dtype=torch.float64) * 2.0 / self.rotary_dim)
+        where = lambda turns: self.rotary_dim * math.log(self.original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+        lo = max(math.floor(where(self.fast)), 0)
+        hi = min(math.ceil(where(self.slow)), self.rotary_dim - 1)
+        ramp = ((torch.arange(half, dtype=torch.float64) - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        return plain / self.factor * ramp + plain * (1.0 - ramp)
+
+    def table(self, max_positions: int) -> torch.Tensor:
+        """float32 [max_positions, rotary_dim]: cos in the first half of each row, sin in the second, both times the magnitude."""
+        angles = torch.arange(max_positions, dtype=torch.float64)[:, None] * self.frequencies()[None, :]
+        return (torch.cat((angles.cos(), angles.sin()), dim=-1) * self.magnitude).to(torch.float32).contiguous().to(self.runtime.device)
+
+
 @register_position("none")
 class NoPosition:
     def __init__(self, params, runtime: Runtime) -> None:
