@@ -92,9 +92,8 @@ class ConvAttention:
             out[n["q_bias"]] = TensorSpec((nq * d,), role="vector", init_std=0.1)
             out[n["k_bias"]] = TensorSpec((nkv * d,), role="vector", init_std=0.1)
             out[n["o_bias"]] = TensorSpec((hidden,), role="vector", init_std=0.1)
-        # a convolution of one tap is a factor per channel; a model may leave such tensors out (all ones)
-        out[n["q_conv"]] = TensorSpec((nq * d, taps), role="vector", init_std=0.3, init_mean=0.3, optional=taps == 1)
-        out[n["k_conv"]] = TensorSpec((nkv * d, taps), role="vector", init_std=0.3, init_mean=0.3, optional=taps == 1)
+        out[n["q_conv"]] = TensorSpec((nq * d, taps), role="vector", init_std=0.3, init_mean=0.3)
+        out[n["k_conv"]] = TensorSpec((nkv * d, taps), role="vector", init_std=0.3, init_mean=0.3)
         return out
 
     def load(self, source) -> None:
@@ -113,11 +112,7 @@ class ConvAttention:
             bias[:self.channels] = torch.cat([source(n["q_bias"]).float().cpu(), source(n["k_bias"]).float().cpu()], dim=0)
             self.proj.set_bias(bias)
             self.o.set_bias(source(n["o_bias"]))
-        pieces = []
-        for key, channels in (("q_conv", self.nq * self.d), ("k_conv", self.nkv * self.d)):
-            stored = source(n[key])
-            pieces.append(stored.float().cpu() if stored is not None else torch.ones(channels, self.taps))
-        self.conv = to_device(torch.cat(pieces, dim=0), torch.float32, device)
+        self.conv = to_device(torch.cat([source(n["q_conv"]).float().cpu(), source(n["k_conv"]).float().cpu()], dim=0), torch.float32, device)
         slopes = [2.0 ** (-self.slope_bits * (h + 1) / self.nq) for h in range(self.nq)]
         self.slopes = torch.tensor(slopes, dtype=torch.float32, device=device)
 

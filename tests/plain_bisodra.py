@@ -103,15 +103,16 @@ def yarn_frequencies(rot, dtype=torch.float64):
 
 
 def rotate_half(x, positions, rot):
-    """x [T, ..., dims]: element i turns with element i + dims / 2 by the angle p f_i."""
+    """x [T, ..., n >= dims]: of the first ``dims`` elements, element i turns with element i + dims / 2 by the angle p f_i."""
     f, magnitude = yarn_frequencies(rot)
     angles = positions.to(torch.float64)[:, None] * f[None, :]
     cos, sin = (angles.cos() * magnitude).to(x.dtype), (angles.sin() * magnitude).to(x.dtype)
     while cos.dim() < x.dim():
         cos, sin = cos.unsqueeze(1), sin.unsqueeze(1)
-    half = x.shape[-1] // 2
-    u, v = x[..., :half], x[..., half:]
-    return torch.cat([u * cos - v * sin, v * cos + u * sin], dim=-1)
+    dims = int(rot["dims"])
+    half = dims // 2
+    u, v, rest = x[..., :half], x[..., half:dims], x[..., dims:]          # elements beyond the first ``dims`` pass unchanged
+    return torch.cat([u * cos - v * sin, v * cos + u * sin, rest], dim=-1)
 
 
 def latent_of(h, tensors, prefix, mixer, eps):
