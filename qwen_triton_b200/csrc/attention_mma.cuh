@@ -53,7 +53,21 @@ struct MmaParams {
     int chunk = 0;
     // Value heads: the value cache is [pages, nv, 64, d] and key head g reads value head g % nv (0: nv = nkv).
     int nv = 0;
+    // With r1 alone (r2 null) the penalty is linear: the score loses r1[h] * (i - j), taken off the unscaled score as
+    // (r1 / scale) * distance.
+    // keep_first > 0 (with a window, no ring): the keys at positions below it stay visible to every later query.
+    int keep_first = 0;
+    // sink: the softmax has one more term of score 0 that carries no value, p_j = e^{s_j} / (1 + sum e^{s_j}).
+    int sink = 0;
 };
+
+// The factor on a row's accumulator and its new denominator when the sink term joins a softmax whose running maximum
+// (scaled, base 2) is m and whose sum relative to m is l; formed around max(m, 0) so that no exponential overflows.
+__device__ __forceinline__ void join_sink(float m, float& l, float& factor) {
+    const float top = fmaxf(m, 0.f);
+    factor = exp2f(m - top);
+    l = l * factor + exp2f(-top);
+}
 
 __device__ __forceinline__ int chunk_start(int pos, int chunk) { return chunk > 0 ? pos / chunk * chunk : 0; }
 
@@ -399,10 +413,18 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
     const int lo = max(p.window > 0 ? max(0, len - p.window) : 0, chunk_start(len - 1, p.chunk));
     const int nv = p.nv > 0 ? p.nv : p.nkv, vh = kvh % nv;
     const int first_tile = lo / WS_TILE, last_tile = (len - 1) / WS_TILE;
-    const int per_stream = (last_tile - first_tile + n_streams) / n_streams;
-    const int tile_begin = first_tile + stream * per_stream;
-    const int n_tiles = max(0, min(last_tile + 1, tile_begin + per_stream) - tile_begin);
+    // the kept first keys' tiles that lie wholly before the window's first tile come first in the walk: tile number u of
+    // the walk is tile u of the sequence below n_keep and tile u + gap from there on
+    const int keep_first = p.window > 0 ? p.keep_first : 0;
+    const int n_keep = min((keep_first + WS_TILE - 1) / WS_TILE, first_tile);
+    const int gap = first_tile - n_keep;
+    const int walk_tiles = last_tile - gap + 1;
+    const int per_stream = (walk_tiles + n_streams - 1) / n_streams;
+    const int tile_begin = stream * per_stream;
+    const int n_tiles = max(0, min(walk_tiles, tile_begin + per_stream) - tile_begin);
     const int* table = p.block_table + (size_t)seq * p.max_blocks;
+    const bool values_are_keys = p.v_cache == p.k_cache && nv == p.nkv;      // one copy per tile serves both products
+    auto tile_of = [&](int u) { return u < n_keep ? u : u + gap; };
 
     const WarpTileCopy copy(d, lds, lane);
     // Page numbers of 32 tiles at a time, one per lane: a table lookup in front of every tile's copy would put an L2
@@ -413,20 +435,21 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
             if ((tile >> 5) != pages_from) {
                 pages_from = tile >> 5;
                 const int mine = min((pages_from << 5) + lane, n_tiles - 1);
-                lane_page = cache_page(table, (tile_begin + mine) >> 1, p.ring_tokens);
+                lane_page = cache_page(table, tile_of(tile_begin + mine) >> 1, p.ring_tokens);
             }
-            const int t32 = tile_begin + tile;
+            const int t32 = tile_of(tile_begin + tile);
             const int page = __shfl_sync(0xffffffffu, lane_page, tile & 31);
             const size_t off = (((size_t)page * p.nkv + kvh) * PAGE + (t32 & 1) * WS_TILE) * d;
             const uint32_t dst = ring0 + (uint32_t)(tile & 1) * 2u * tile_bytes;
             copy.template start<DMAX, EXACT>(dst, p.k_cache + off);
-            copy.template start<DMAX, EXACT>(dst + tile_bytes, p.v_cache + (((size_t)page * nv + vh) * PAGE + (t32 & 1) * WS_TILE) * d);
+            if (!values_are_keys)
+                copy.template start<DMAX, EXACT>(dst + tile_bytes, p.v_cache + (((size_t)page * nv + vh) * PAGE + (t32 & 1) * WS_TILE) * d);
         }
         cp_async_commit();
     };
     // Keys and values of earlier positions do not depend on the kernel before this one (it writes only the new
     // token's row, which lies in the last tile): a first tile that is not the last is requested before the wait.
-    const bool early = n_tiles > 0 && tile_begin < last_tile;
+    const bool early = n_tiles > 0 && tile_of(tile_begin) < last_tile;
     if (early) issue(0);
     pdl_wait();
     for (int i = tid; i < 16 * (d >> 3); i += blockDim.x) {                          // query rows, zero beyond the group
@@ -446,10 +469,14 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
     for (int i = 0; i < DMAX / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     const float scale2 = p.scale * LOG2E;                            // positive (checked by the host)
     float pen_c[2] = {0.f, 0.f}, pen_r2[2] = {0.f, 0.f};             // of this thread's two rows (query heads g and g + 8)
+    const bool pen_linear = PEN && p.r2 == nullptr;
     if (PEN) {
 #pragma unroll
         for (int r = 0; r < 2; ++r)
-            if (g + 8 * r < rows) { pen_c[r] = p.r1[head_base + g + 8 * r] / scale2; pen_r2[r] = p.r2[head_base + g + 8 * r]; }
+            if (g + 8 * r < rows) {
+                pen_c[r] = p.r1[head_base + g + 8 * r] / (pen_linear ? p.scale : scale2);
+                pen_r2[r] = pen_linear ? 0.f : p.r2[head_base + g + 8 * r];
+            }
     }
     const int mi = lane >> 3;
     const uint32_t k_lane = (uint32_t)(((mi >> 1) * 8 + (lane & 7)) * lds + (mi & 1) * 8) * 2u;
@@ -460,8 +487,8 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
         issue(tile + 1);                                             // into the stage that the tile before this one used
         cp_async_wait<1>();
         __syncwarp();
-        const uint32_t k_s = ring0 + (uint32_t)(tile & 1) * 2u * tile_bytes, v_s = k_s + tile_bytes;
-        const int pos0 = (tile_begin + tile) * WS_TILE;
+        const uint32_t k_s = ring0 + (uint32_t)(tile & 1) * 2u * tile_bytes, v_s = values_are_keys ? k_s : k_s + tile_bytes;
+        const int pos0 = tile_of(tile_begin + tile) * WS_TILE;
         float s[4][4] = {};
 #pragma unroll
         for (int ks = 0; ks < DMAX / 16; ++ks) {
@@ -475,7 +502,13 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
                 mma_bf16(s[3], qf[ks], b1[2], b1[3]);
             }
         }
-        if (PEN) {                                                   // entries beyond the sequence are overwritten below
+        if (PEN && pen_linear) {                                     // entries beyond the sequence are overwritten below
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    s[nt][e] -= pen_c[e >> 1] * (float)(len - 1 - (pos0 + nt * 8 + 2 * t + (e & 1)));
+        } else if (PEN) {
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
@@ -488,7 +521,7 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int pos = pos0 + nt * 8 + 2 * t + (e & 1);
-                    if (pos < lo || pos >= len) s[nt][e] = -INFINITY;
+                    if ((pos < lo && pos >= keep_first) || pos >= len) s[nt][e] = -INFINITY;
                 }
         }
         float alpha[2];
@@ -571,7 +604,9 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
         }
         const int head = head_base + r;
         if (gridDim.x == 1) {
-            p.out[((size_t)seq * p.nq + head) * d + c] = __float2bfloat16_rn(a_all / l_all);
+            float factor = 1.f;
+            if (p.sink) join_sink(m_all, l_all, factor);
+            p.out[((size_t)seq * p.nq + head) * d + c] = __float2bfloat16_rn(a_all * factor / l_all);
         } else if (p.cluster_merge) {
             float* slot = inbox + (size_t)split * inbox_stride;
             cluster_store_float(slot + i, 0, a_all);
@@ -598,7 +633,9 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
                     l_all += slot[rows * d + 2 * r + 1] * f;
                     a_all += slot[i] * f;
                 }
-                p.out[((size_t)seq * p.nq + head_base + r) * d + (i % d)] = __float2bfloat16_rn(a_all / l_all);
+                float factor = 1.f;
+                if (p.sink) join_sink(m_all, l_all, factor);
+                p.out[((size_t)seq * p.nq + head_base + r) * d + (i % d)] = __float2bfloat16_rn(a_all * factor / l_all);
             }
         }
     }
@@ -606,7 +643,7 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
 
 // One block per (sequence, head): out = sum_s acc_s e^{m_s - m} / sum_s l_s e^{m_s - m}; empty splits have m = -inf.
 __global__ void attention_combine_mma_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                             __nv_bfloat16* __restrict__ out, int n_splits, int d) {
+                                             __nv_bfloat16* __restrict__ out, int n_splits, int d, int sink) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t item = blockIdx.x;
@@ -617,13 +654,19 @@ __global__ void attention_combine_mma_kernel(const float* __restrict__ part_acc,
         const float ms = part_ml[(item * n_splits + s) * 2];
         l_all += ms == -INFINITY ? 0.f : part_ml[(item * n_splits + s) * 2 + 1] * __expf(ms - m_all);
     }
+    float factor = 1.f;
+    if (sink) {                                                      // the maxima are in the natural-log domain here
+        const float top = fmaxf(m_all, 0.f);
+        factor = __expf(m_all - top);
+        l_all = l_all * factor + __expf(-top);
+    }
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float a = 0.f;
         for (int s = 0; s < n_splits; ++s) {
             const float ms = part_ml[(item * n_splits + s) * 2];
             if (ms != -INFINITY) a += part_acc[(item * n_splits + s) * d + c] * __expf(ms - m_all);
         }
-        out[item * d + c] = __float2bfloat16_rn(a / l_all);
+        out[item * d + c] = __float2bfloat16_rn(a * factor / l_all);
     }
 }
 
@@ -654,7 +697,14 @@ __global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const Mma
     const int p_first = past + q0, p_last = past + q0 + rows - 1;
     const int lo = max(p.window > 0 ? max(0, p_first - p.window + 1) : 0, chunk_start(p_first, p.chunk));
     const int nv = p.nv > 0 ? p.nv : p.nkv, vh = kvh % nv;
-    const int page_begin = lo / PAGE, n_tiles = p_last / PAGE - page_begin + 1;
+    // the kept first keys' pages that lie wholly before the window's first page come first: tile number u of the walk is
+    // page u of the sequence below n_keep and page u + gap from there on
+    const int keep_first = p.window > 0 ? p.keep_first : 0;
+    const int n_keep = min((keep_first + PAGE - 1) / PAGE, lo / PAGE);
+    const int gap = lo / PAGE - n_keep;
+    const int n_tiles = p_last / PAGE - gap + 1;
+    const bool values_are_keys = p.v_cache == p.k_cache && nv == p.nkv;              // one copy per tile serves both products
+    auto page_of = [&](int u) { return u < n_keep ? u : u + gap; };
 
     for (int i = tid; i < PF_BQ * (d >> 3); i += 128) {                              // query tile, rows beyond the sequence zero
         const int r = i / (d >> 3), c = i % (d >> 3);
@@ -665,11 +715,11 @@ __global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const Mma
     const TileCopy copy(d, lds, tid);
     auto issue = [&](int tile) {
         if (tile < n_tiles) {
-            const int page = cache_page(table, page_begin + tile, p.ring_tokens);
+            const int page = cache_page(table, page_of(tile), p.ring_tokens);
             const size_t off = ((size_t)page * p.nkv + kvh) * PAGE * d;
             const uint32_t dst = kv0 + (uint32_t)(tile & 1) * 2u * tile_bytes;
             copy.start(dst, p.k_cache + off);
-            copy.start(dst + tile_bytes, p.v_cache + ((size_t)page * nv + vh) * PAGE * d);
+            if (!values_are_keys) copy.start(dst + tile_bytes, p.v_cache + ((size_t)page * nv + vh) * PAGE * d);
         }
         cp_async_commit();
     };
@@ -684,7 +734,8 @@ __global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const Mma
 #pragma unroll
     for (int i = 0; i < DMAX / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     const float scale2 = p.scale * LOG2E;
-    const float pen_c = PEN ? p.r1[head] / scale2 : 0.f, pen_r2 = PEN ? p.r2[head] : 0.f;
+    const bool pen_linear = PEN && p.r2 == nullptr;
+    const float pen_c = PEN ? p.r1[head] / (pen_linear ? p.scale : scale2) : 0.f, pen_r2 = PEN && !pen_linear ? p.r2[head] : 0.f;
     // absolute positions of this thread's two query rows; rows beyond the sequence act as its last row
     const int qpos[2] = {min(past + q0 + warp * 16 + g, p_last), min(past + q0 + warp * 16 + g + 8, p_last)};
     const int warp_pos_min = min(past + q0 + warp * 16, p_last), warp_pos_max = min(past + q0 + warp * 16 + 15, p_last);
@@ -695,9 +746,10 @@ __global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const Mma
         issue(tile + 1);
         cp_async_wait<1>();
         __syncthreads();
-        const uint32_t k_s = kv0 + (uint32_t)(tile & 1) * 2u * tile_bytes, v_s = k_s + tile_bytes;
-        const int pos0 = (page_begin + tile) * PAGE;
-        const bool any_visible = pos0 <= warp_pos_max && (p.window <= 0 || pos0 + PAGE - 1 > warp_pos_min - p.window) && pos0 + PAGE - 1 >= warp_lo_min;
+        const uint32_t k_s = kv0 + (uint32_t)(tile & 1) * 2u * tile_bytes, v_s = values_are_keys ? k_s : k_s + tile_bytes;
+        const int pos0 = page_of(tile) * PAGE;
+        const bool any_visible = pos0 <= warp_pos_max && (p.window <= 0 || pos0 + PAGE - 1 > warp_pos_min - p.window || pos0 < keep_first) &&
+                                 pos0 + PAGE - 1 >= warp_lo_min;
         if (any_visible) {
             float s[8][4];
 #pragma unroll
@@ -721,8 +773,15 @@ __global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const Mma
             // Scores stay unscaled; the scale is folded into the exponent: p = 2^(s * scale2 - m * scale2), one FMA
             // and one ex2 per score.  Most tiles lie wholly below the diagonal (and inside the window) for every row
             // of the warp and need no mask.
-            const bool all_visible = pos0 + PAGE - 1 <= warp_pos_min && (p.window <= 0 || pos0 > warp_pos_max - p.window) && pos0 >= warp_lo_max;
-            if (PEN) {                                               // keys ahead of a row's query are overwritten by the mask below
+            const bool all_visible = pos0 + PAGE - 1 <= warp_pos_min &&
+                                     (p.window <= 0 || pos0 > warp_pos_max - p.window || pos0 + PAGE - 1 < keep_first) && pos0 >= warp_lo_max;
+            if (PEN && pen_linear) {                                 // keys ahead of a row's query are overwritten by the mask below
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        s[nt][e] -= pen_c * (float)(qpos[e >> 1] - (pos0 + nt * 8 + 2 * t + (e & 1)));
+            } else if (PEN) {
 #pragma unroll
                 for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
@@ -737,7 +796,7 @@ __global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const Mma
                     for (int e = 0; e < 4; ++e) {
                         const int pos = pos0 + nt * 8 + 2 * t + (e & 1);
                         const int qp = qpos[e >> 1];
-                        const bool visible = pos <= qp && (p.window <= 0 || pos > qp - p.window) && pos >= qlo[e >> 1];
+                        const bool visible = pos <= qp && (p.window <= 0 || pos > qp - p.window || pos < keep_first) && pos >= qlo[e >> 1];
                         if (!visible) s[nt][e] = -INFINITY;
                     }
             }
@@ -791,7 +850,9 @@ __global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const Mma
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
         const int row = warp * 16 + g + 8 * r;
         if (row < rows) {
-            const float inv = 1.f / l[r];
+            float factor = 1.f;
+            if (p.sink) join_sink(m[r], l[r], factor);
+            const float inv = factor / l[r];
             __nv_bfloat16* dst = p.out + ((size_t)(q_begin + q0 + row) * p.nq + head) * d;
 #pragma unroll
             for (int nt = 0; nt < DMAX / 8; ++nt)

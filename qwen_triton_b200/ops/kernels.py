@@ -86,9 +86,10 @@ _SIGNATURES = {
         "qt_attention_decode_mma": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                                     _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr],
         "qt_attention_decode_ws": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
-                                   _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+                                   _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
+                                   _c_int, _c_int, _c_ptr],
         "qt_attention_prefill_mma": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
-                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     },
     "attention_tc": {
         "qt_attention_prefill_tc": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
@@ -704,13 +705,21 @@ def _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_t
     return tokens, num_heads, head_dim
 
 
-def _generic_only(penalty, keep_first: int, sink: bool, v_dim, impl: str | None) -> bool:
-    """Whether a call asks for what only the generic attention kernels compute: a linear distance penalty (``penalty`` =
-    (slopes, None)), kept first keys, a softmax sink, or values that are the head of the cached key rows."""
-    special = (penalty is not None and penalty[1] is None) or keep_first > 0 or sink or v_dim is not None
-    if special and impl not in (None, "generic"):
-        raise KernelError(f"attention kernel {impl!r} takes no linear penalty, kept first keys, sink or values inside the key rows")
-    return special
+def _extended_choice(q, k_cache, v_cache, page_tokens: int, ring_tokens: int, scale: float, penalty, keep_first: int, sink: bool, v_dim,
+                     chunk, impl: str | None, mma: str) -> str | None:
+    """The kernel for a call that asks for a linear distance penalty (``penalty`` = (slopes, None)), kept first keys, a
+    softmax sink, or values that are the head of the cached key rows; None for a call that asks for none of these.  The
+    mma.sync kernels (``mma`` names the caller's) compute the first three for values as wide as the keys; the generic
+    kernels compute all four."""
+    if not ((penalty is not None and penalty[1] is None) or keep_first > 0 or sink or v_dim is not None):
+        return None
+    fits = (v_dim is None and v_cache.shape[-1] == q.shape[2] and attention_mma_supported(q, page_tokens) and scale > 0
+            and not (keep_first > 0 and (ring_tokens or chunk)))
+    if impl in (None, mma) and fits:
+        return mma
+    if impl in (None, "generic"):
+        return "generic"
+    raise KernelError(f"attention kernel {impl!r} does not take this call (linear penalty, kept first keys, sink or values inside the key rows)")
 
 
 def _plain_attention(q: torch.Tensor, v_cache: torch.Tensor, penalty) -> bool:
@@ -780,8 +789,9 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     of score 0 without a value.  ``v_dim``: the values are the first ``v_dim`` elements of the rows of ``v_cache`` (which
     may be the key cache itself)."""
     _, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty, v_dim)
-    if _generic_only(penalty, keep_first, sink, v_dim, impl):
-        impl = "generic"
+    extended = _extended_choice(q, k_cache, v_cache, page_tokens, ring_tokens, scale, penalty, keep_first, sink, v_dim, chunk, impl, "mma")
+    if extended is not None:
+        impl = extended
     elif not _plain_attention(q, v_cache, penalty):
         impl = _penalised_choice(q, v_cache, page_tokens, scale, impl, "mma")
     n_seqs = seq_past.shape[0]
@@ -801,7 +811,8 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         _call("attention_mma", "qt_attention_prefill_mma", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out),
               _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, int(max_q_len), num_heads,
               num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale),
-              _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, int(chunk or 0), v_cache.shape[1], _stream())
+              _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, int(chunk or 0), v_cache.shape[1],
+              int(keep_first), 1 if sink else 0, _stream())
         return
     _call("attention", "qt_attention_prefill", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q, "q"),
           _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, int(max_q_len), num_heads,
@@ -840,8 +851,9 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     _need(seq_len, "seq_len", torch.int32, (n_seqs,))
     if impl == "mma" and _special_mask(k_cache, v_cache, chunk):
         raise KernelError("the block-tile decode kernel takes no mask in chunks and no value heads shared by several key heads")
-    if _generic_only(penalty, keep_first, sink, v_dim, impl):
-        impl = "generic"
+    extended = _extended_choice(q, k_cache, v_cache, page_tokens, ring_tokens, scale, penalty, keep_first, sink, v_dim, chunk, impl, "ws")
+    if extended is not None:
+        impl = extended
     elif not _plain_attention(q, v_cache, penalty):
         impl = _penalised_choice(q, v_cache, page_tokens, scale, impl, "ws")
     if n_splits > 1:
@@ -862,7 +874,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     if picked == "ws":
         _call("attention_mma", "qt_attention_decode_ws", *common, int(warps), _ptr(part_acc), _ptr(part_ml),
               _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, int(chunk or 0), v_cache.shape[1],
-              _stream(), launches=launches)
+              int(keep_first), 1 if sink else 0, _stream(), launches=launches)
     elif picked == "mma":
         _call("attention_mma", "qt_attention_decode_mma", *common, _ptr(part_acc), _ptr(part_ml), _stream(), launches=launches)
     else:

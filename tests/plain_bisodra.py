@@ -49,9 +49,10 @@ def slopes(heads: int, dtype):
     return torch.tensor([2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)], dtype=dtype)
 
 
-def visible_window(T: int, size: int, keep_first: int):
-    """[T, T] bool: query i sees key j <= i if it is within ``size`` positions or among the first ``keep_first``."""
-    i = torch.arange(T)[:, None]
+def visible_window(T: int, size: int, keep_first: int, rows=None):
+    """[rows, T] bool: the query at position i (``rows``; every position 0..T-1 by default) sees key j <= i if it is
+    within ``size`` positions or among the first ``keep_first``."""
+    i = (torch.arange(T) if rows is None else torch.as_tensor(rows))[:, None]
     j = torch.arange(T)[None, :]
     return (j <= i) & ((i - j < size) | (j < keep_first))
 
@@ -64,6 +65,22 @@ def softmax_with_sink(scores, visible):
     return e / (torch.exp(-top) + e.sum(dim=-1, keepdim=True))
 
 
+def biased_heads(q, k, rows, scale, size, keep_first):
+    """Queries q [n, H, d] at positions ``rows`` over the keys k [T, G, d] of their sequence, which are the values too:
+    score = q . k * scale - slope_h (i - j), a window that keeps the first keys, softmax with a sink.  [n, H, d]."""
+    heads, groups = q.shape[1], k.shape[1]
+    rows = torch.as_tensor(rows)
+    visible = visible_window(k.shape[0], size if size is not None else k.shape[0], keep_first, rows)
+    distance = (rows[:, None] - torch.arange(k.shape[0])[None, :]).to(q.dtype)
+    slope = slopes(heads, q.dtype)
+    out = torch.zeros_like(q)
+    for head in range(heads):
+        kv = k[:, head // (heads // groups)]
+        scores = (q[:, head] @ kv.T) * scale - slope[head] * distance
+        out[:, head] = softmax_with_sink(scores, visible) @ kv
+    return out
+
+
 def window_attention(h, tensors, prefix, mixer):
     """Grouped heads; biased q, k and o; a short convolution on q and k; values are the keys; a linear distance bias;
     a window that keeps the first tokens; softmax with a sink; a sigmoid gate on the heads' outputs."""
@@ -74,14 +91,7 @@ def window_attention(h, tensors, prefix, mixer):
     q = short_conv(h @ t("q").T + t("q.b"), t("q.conv")).view(T, heads, dim)
     k = short_conv(h @ t("k").T + t("k.b"), t("k.conv")).view(T, groups, dim)
     mask = mixer.get("mask") or {}
-    visible = visible_window(T, int(mask.get("size", T)), int(mask.get("keep_first", 0)))
-    distance = (torch.arange(T)[:, None] - torch.arange(T)[None, :]).to(dt)
-    slope = slopes(heads, dt)
-    out = h.new_zeros(T, heads, dim)
-    for head in range(heads):
-        kv = k[:, head // (heads // groups)]
-        scores = (q[:, head] @ kv.T) * float(mixer["scale"]) - slope[head] * distance
-        out[:, head] = softmax_with_sink(scores, visible) @ kv
+    out = biased_heads(q, k, torch.arange(T), float(mixer["scale"]), mask.get("size"), int(mask.get("keep_first", 0)))
     gated = out.reshape(T, heads * dim) * torch.sigmoid(h @ t("g").T)
     return gated @ t("o").T + t("o.b")
 
@@ -126,6 +136,22 @@ def latent_of(h, tensors, prefix, mixer, eps):
     return c, shared
 
 
+def latent_heads(q_plain, q_turned, c, shared, w_uk, w_uv, rows, scale):
+    """Queries at positions ``rows`` (q_plain [n, H, d], q_turned [n, H, r] already rotated) over the kept rows of their
+    sequence (c [T, rank], shared [T, r]): head h has the keys W_uk_h c | shared and the values W_uv_h c; causal, plain
+    softmax.  w_uk [H d, rank], w_uv [H dv, rank].  [n, H, dv]."""
+    heads, dim = q_plain.shape[1], q_plain.shape[2]
+    T = c.shape[0]
+    k_plain = (c @ w_uk.T).view(T, heads, dim)
+    values = (c @ w_uv.T).view(T, heads, -1)
+    causal = torch.arange(T)[None, :] <= torch.as_tensor(rows)[:, None]
+    out = q_plain.new_zeros(q_plain.shape[0], heads, values.shape[-1])
+    for head in range(heads):
+        scores = (q_plain[:, head] @ k_plain[:, head].T + q_turned[:, head] @ shared.T) * scale
+        out[:, head] = torch.softmax(scores.masked_fill(~causal, float("-inf")), dim=-1) @ values[:, head]
+    return out
+
+
 def latent_attention(h, tensors, prefix, mixer, eps, kept):
     """Queries through a latent of their own; keys and values expanded per head from ``kept`` = (c, shared rotated
     key part); causal softmax; a sigmoid gate on the heads' outputs."""
@@ -137,13 +163,7 @@ def latent_attention(h, tensors, prefix, mixer, eps, kept):
     cq = rms_norm(h @ t("dq").T, t("dq.norm"), eps)
     q = (cq @ t("uq").T).view(T, heads, dim + rot_dim)
     q_plain, q_turned = q[..., :dim], rotate_half(q[..., dim:], torch.arange(T), mixer["rot"])
-    k_plain = (c @ t("uk").T).view(T, heads, dim)
-    values = (c @ t("uv").T).view(T, heads, vdim)
-    causal = torch.arange(T)[None, :] <= torch.arange(T)[:, None]
-    out = h.new_zeros(T, heads, vdim)
-    for head in range(heads):
-        scores = (q_plain[:, head] @ k_plain[:, head].T + q_turned[:, head] @ shared.T) * float(mixer["scale"])
-        out[:, head] = torch.softmax(scores.masked_fill(~causal, float("-inf")), dim=-1) @ values[:, head]
+    out = latent_heads(q_plain, q_turned, c, shared, t("uk"), t("uv"), torch.arange(T), float(mixer["scale"]))
     gated = out.reshape(T, heads * vdim) * torch.sigmoid(h @ t("g").T)
     return gated @ t("o").T
 
