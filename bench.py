@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the Qwen3-8B shape on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl b200|reference] [--temperature T]
-    python bench.py --workload 0.6b-unequal | 32b-long | lederax-layers | vunepel-layers
+    python bench.py --workload 0.6b-unequal | 32b-long | lederax-layers | vunepel-layers | bisodra-layers
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 from a 2,048-token cache,
 timed on the device over the decode steps (step function plus greedy sampling kernel, tokens given
@@ -22,7 +22,9 @@ dense model of the same width, heads, window and as many weights read per token:
 at batch 8 and 64, each with its share of the measured peaks), ``vunepel-layers`` (the same for four layers of the
 Vunepel design: differential attention with a dense feed-forward, two gated-delta-rule layers with routed experts, an
 attention layer that reads the first one's keys and values; ``--size``, ``--arm`` and ``--phase`` run one of its
-measurements alone, for a profiler).
+measurements alone, for a profiler), ``bisodra-layers`` (the same for four layers of the Bisodra design: attention through
+a latent, attention with a short convolution on q and k under a window with kept first keys, a latent layer that reads the
+first one's cache rows, a second convolution layer; the same three options).
 """
 from __future__ import annotations
 
@@ -56,10 +58,10 @@ def parse_args():
     parser.add_argument("--no-prefill", action="store_true")
     parser.add_argument("--min-seconds", type=float, default=2.0, help="a timed region lasts at least this long")
     parser.add_argument("--temperature", type=float, default=0.0, help="sampling temperature of the end-to-end run (0: greedy)")
-    parser.add_argument("--workload", default=None, choices=["0.6b-unequal", "32b-long", "lederax-layers", "vunepel-layers"])
-    parser.add_argument("--size", default=None, help="vunepel-layers: only the size whose name starts with this")
-    parser.add_argument("--arm", default=None, choices=["vunepel", "dense"], help="vunepel-layers: only this model")
-    parser.add_argument("--phase", default=None, choices=["prefill", "decode8", "decode64"], help="vunepel-layers: only this measurement")
+    parser.add_argument("--workload", default=None, choices=["0.6b-unequal", "32b-long", "lederax-layers", "vunepel-layers", "bisodra-layers"])
+    parser.add_argument("--size", default=None, help="vunepel-layers, bisodra-layers: only the size whose name starts with this")
+    parser.add_argument("--arm", default=None, choices=["vunepel", "bisodra", "dense"], help="vunepel-layers, bisodra-layers: only this model")
+    parser.add_argument("--phase", default=None, choices=["prefill", "decode8", "decode64"], help="vunepel-layers, bisodra-layers: only this measurement")
     return parser.parse_args()
 
 
@@ -322,6 +324,109 @@ def run_vunepel_layers(args) -> dict:
             "sizes": out}
 
 
+BISODRA_SIZES = (
+    # name, width, latent heads, plain and rotated query/key size, value size, query latent, key/value latent,
+    # convolution-attention heads, kv heads, head size, window, kept first keys, feed-forward width
+    ("w2048-latent16x128+64-r512-conv16x128-win1024-ff8192", 2048, 16, 128, 64, 128, 768, 512, 16, 4, 128, 1024, 64, 8192),
+    ("w4096-latent32x128+64-r512-conv32x128-win4096-ff16384", 4096, 32, 128, 64, 128, 1536, 512, 32, 8, 128, 4096, 128, 16384),
+    ("w1024-latent8x64+32-r256-conv8x64-win512-ff4096", 1024, 8, 64, 32, 64, 384, 256, 8, 8, 64, 512, 16, 4096),
+)
+
+
+def run_bisodra_layers(args) -> dict:
+    """Prefill and one-token steps of four Bisodra layers at sizes that resemble a real model's (attention through a
+    latent; attention with a short convolution on q and k, a window with kept first keys, a distance bias and a sink; a
+    latent layer that reads the first one's cache rows; a second convolution layer; each with a feed-forward of two
+    matrices), and of the Qwen3 dense layers that come closest: same width and vocabulary, the convolution layers' heads,
+    kv heads and head size, full attention in the first two layers and the same window in the last two, and a gated
+    feed-forward that reads as many weights per token."""
+    import torch
+
+    from qwen_triton_b200 import QwenB200ForCausalLM, config_from_dict
+
+    peak, peak_source = peaks()
+    vocab, prompt_len = 32768, args.prompt_len
+    out = []
+    for size in BISODRA_SIZES:
+        name, width, l_heads, l_dim, l_rot, l_vdim, q_rank, kv_rank, heads, kv_heads, dim, window, keep, ff = size
+        if args.size and not name.startswith(args.size):
+            continue
+        rot = {"base": 1000000.0, "dims": l_rot, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+        latent = {"heads": l_heads, "dim": l_dim, "rot_dim": l_rot, "vdim": l_vdim, "q_rank": q_rank, "kv_rank": kv_rank,
+                  "scale": (l_dim + l_rot) ** -0.5, "rot": rot}
+        conv = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "conv": 4,
+                "mask": {"size": window, "keep_first": keep}}
+        mlp = {"kind": "dense", "ff": ff}
+        bisodra = {"architecture": "Bisodra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+                   "logit_scale": 1.0,
+                   "layers": [{"type": "latent_attention", "mixer": latent, "mlp": mlp}, {"type": "attention", "mixer": conv, "mlp": mlp},
+                              {"type": "latent_attention", "mixer": {**latent, "kv_from": 0}, "mlp": mlp},
+                              {"type": "attention", "mixer": conv, "mlp": mlp}]}
+        layers = 4
+        row = kv_rank + l_rot
+        # weights a token multiplies with, per layer kind (the per-head matrices of a latent layer once each)
+        latent_reader = width * (q_rank + l_heads * l_vdim) + q_rank * l_heads * (l_dim + l_rot) + l_heads * kv_rank * (l_dim + l_vdim) \
+            + l_heads * l_vdim * width
+        latent_own = latent_reader + width * row
+        conv_w = width * (2 * heads + kv_heads) * dim + heads * dim * width
+        token_weights = latent_own + latent_reader + 2 * conv_w + layers * 2 * width * ff
+        inter = max(64, round(2 * ff / 3 / 64) * 64)
+        dense = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": vocab, "hidden_size": width,
+                 "intermediate_size": inter, "num_hidden_layers": layers, "num_attention_heads": heads,
+                 "num_key_value_heads": kv_heads, "head_dim": dim, "max_position_embeddings": 32768,
+                 "use_sliding_window": True, "sliding_window": window, "max_window_layers": 2}
+        dense_token = layers * (width * (heads + 2 * kv_heads) * dim + heads * dim * width + 3 * width * inter)
+        entry = {"size": name, "layers": layers, "dense_intermediate": inter}
+
+        def mean_keys(length, span, kept):
+            """Keys a query of a prompt sees on average: all earlier ones, or the window's and the kept first ones."""
+            if span is None:
+                return (length + 1) / 2
+            return sum(min(i + 1, span) + max(0, min(kept, i + 1 - span)) for i in range(length)) / length
+
+        def live_keys(context, span, kept):
+            return context if span is None else min(context, span + max(0, min(kept, context - span)))
+
+        # per key and query token: attention FLOPs (scores and values), and bytes of cache a one-token step reads per key
+        arms = (("bisodra", bisodra, token_weights,
+                 ((2 * l_heads * (row + kv_rank), None, 0, 2 * row), (4 * heads * dim, window, keep, 2 * kv_heads * dim)) * 2),
+                ("dense", dense, dense_token,
+                 ((4 * heads * dim, None, 0, 4 * kv_heads * dim),) * 2 + ((4 * heads * dim, window, 0, 4 * kv_heads * dim),) * 2))
+        for label, raw, per_token, attention in arms:
+            if args.arm and label != args.arm:
+                continue
+            model = QwenB200ForCausalLM.from_config(config_from_dict(raw), seed=1, dtype="bf16",
+                                                    max_tokens=64 * (prompt_len + 512), max_seq_len=prompt_len + 512,
+                                                    max_step_tokens=max(4096, prompt_len), chunk_tokens=prompt_len)
+            result = {}
+            if args.phase in (None, "prefill"):
+                ms = time_prefill(model, prompt_len, vocab, repeats=args.steps if args.phase else 5, warmup=args.warmup if args.phase else 3)
+                flops = 2 * prompt_len * (per_token + vocab * width / prompt_len) \
+                    + sum(f * prompt_len * mean_keys(prompt_len, span, kept) for f, span, kept, _ in attention)
+                result["prefill"] = {"tokens": prompt_len, "ms": round(ms, 3), "tokens_per_s": round(prompt_len * 1e3 / ms),
+                                     "tensor_fraction": round(flops / (ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)}
+            for batch in (8, 64):
+                if args.phase not in (None, f"decode{batch}"):
+                    continue
+                prompts = random_prompts(batch, prompt_len, vocab, 300 + batch)
+                ms, launches, clocks, context, steps = time_decode(model, prompts, args.steps, args.warmup, vocab,
+                                                                   args.min_seconds / 4, 256)
+                read = 2 * (per_token + vocab * width) + batch * sum(b * live_keys(context, span, kept) for _, span, kept, b in attention)
+                result[f"decode_batch{batch}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(batch * 1e3 / ms),
+                                                   "launches_per_step": round(launches / steps, 1), "steps": steps,
+                                                   "hbm_fraction": round(read / (ms * 1e-3) / (peak["hbm_gbs"] * 1e9), 4),
+                                                   "clocks": clocks}
+            entry[label] = result
+            print(f"[bench] {name} {label}: " + json.dumps({k: {a: b for a, b in v.items() if a != 'clocks'} for k, v in result.items()}),
+                  file=sys.stderr, flush=True)
+            del model
+            torch.cuda.empty_cache()
+        out.append(entry)
+    return {"workload": args.workload, "impl": "b200", "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
+            "config": {"prompt_len": prompt_len, "layers": 4, "vocab": vocab, "peaks": peak_source,
+                       "l2": "weights and caches of a step exceed L2 at every size but the smallest"},
+            "sizes": out}
+
 
 def time_prefill(model, tokens: int, vocab: int, repeats: int = 5, warmup: int = 3):
     import torch
@@ -513,6 +618,8 @@ def run_workload(args) -> dict:
         return run_lederax_layers(args)
     if args.workload == "vunepel-layers":
         return run_vunepel_layers(args)
+    if args.workload == "bisodra-layers":
+        return run_bisodra_layers(args)
     import torch
 
     from qwen_triton_b200 import QwenB200ForCausalLM, StepEntry, load_preset
