@@ -71,6 +71,12 @@ _SIGNATURES = {
         "qt_head_product": [_c_ptr, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ll, _c_ll, _c_int,
                             _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     },
+    "attention_latent": {
+        # q, cache, out, block_table, max_blocks, seq_start, seq_past, seq_len, n_seqs, max_q_len, heads, row, rank, page_tokens, scale,
+        # n_splits, part_acc, part_ml, stream
+        "qt_attention_latent": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr],
+    },
     "experts": {
         "qt_experts_by_pair": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                                _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_int, _c_float, _c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr],
@@ -774,6 +780,29 @@ def _pick_attention(q: torch.Tensor, page_tokens: int, impl: str | None, prefill
     return impl
 
 
+def attention_latent_supported(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, num_kv_heads: int, page_tokens: int,
+                               ring_tokens: int, window, scale: float, penalty, chunk, keep_first: int, sink: bool, v_dim) -> bool:
+    """The tensor-core kernel for cached latent rows takes bfloat16, one key head whose rows are the values' source
+    too, rows and value sizes that are multiples of 8 (values up to 512, a row within shared memory), a positive
+    scale, pages of 64 tokens and a plain causal softmax."""
+    return (v_dim is not None and v_cache is k_cache and num_kv_heads == 1 and not ring_tokens and not window and penalty is None
+            and not chunk and not keep_first and not sink and scale > 0 and attention_latent_shape(q.dtype, q.shape[2], v_dim, page_tokens))
+
+
+def attention_latent_shape(dtype: torch.dtype, row: int, rank: int, page_tokens: int) -> bool:
+    """The element type and sizes that the tensor-core kernel for cached latent rows takes (QT_B200_LATENT_MMA=0: none)."""
+    return (dtype == torch.bfloat16 and page_tokens == 64 and row % 8 == 0 and rank % 8 == 0 and 8 <= rank <= min(row, 512)
+            and 3 * 64 * (-(-row // 16) * 16 + 8) * 2 <= 227 * 1024 and not os.environ.get("QT_B200_LATENT_MMA", "1").startswith("0"))
+
+
+def _attention_latent(q, cache, out, block_table, seq_start, seq_past, seq_len, n_seqs, max_q_len, page_tokens, scale, v_dim, n_splits,
+                      part_acc, part_ml) -> None:
+    _call("attention_latent", "qt_attention_latent", _ptr(q), _ptr(cache), _ptr(out), _ptr(block_table), block_table.shape[1],
+          _ptr(seq_start) if seq_start is not None else None, _ptr(seq_past) if seq_past is not None else None,
+          _ptr(seq_len) if seq_len is not None else None, n_seqs, int(max_q_len), q.shape[1], q.shape[2], int(v_dim), page_tokens, float(scale),
+          int(n_splits), _ptr(part_acc) if n_splits > 1 else None, _ptr(part_ml) if n_splits > 1 else None, _stream())
+
+
 def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                       block_table: torch.Tensor, seq_start: torch.Tensor, seq_past: torch.Tensor, max_q_len: int,
                       num_kv_heads: int, page_tokens: int, ring_tokens: int, window: int | None, scale: float,
@@ -789,6 +818,17 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     of score 0 without a value.  ``v_dim``: the values are the first ``v_dim`` elements of the rows of ``v_cache`` (which
     may be the key cache itself)."""
     _, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty, v_dim)
+    if impl in (None, "latent") and attention_latent_supported(q, k_cache, v_cache, num_kv_heads, page_tokens, ring_tokens, window, scale, penalty,
+                                                               chunk, keep_first, sink, v_dim):
+        n_seqs = seq_past.shape[0]
+        _need(seq_start, "seq_start", torch.int32, (n_seqs + 1,))
+        _need(seq_past, "seq_past", torch.int32)
+        if block_table.shape[0] < n_seqs:
+            raise KernelError("attention_prefill: block table has fewer rows than sequences")
+        _attention_latent(q, k_cache, out, block_table, seq_start, seq_past, None, n_seqs, max_q_len, page_tokens, scale, v_dim, 1, None, None)
+        return
+    if impl == "latent":
+        raise KernelError("the tensor-core kernel for cached latent rows does not take this call")
     extended = _extended_choice(q, k_cache, v_cache, page_tokens, ring_tokens, scale, penalty, keep_first, sink, v_dim, chunk, impl, "mma")
     if extended is not None:
         impl = extended
@@ -849,6 +889,17 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     """
     n_seqs, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty, v_dim)
     _need(seq_len, "seq_len", torch.int32, (n_seqs,))
+    if impl in (None, "latent") and attention_latent_supported(q, k_cache, v_cache, num_kv_heads, page_tokens, ring_tokens, window, scale, penalty,
+                                                               chunk, keep_first, sink, v_dim):
+        if n_splits > 1:
+            _need(part_acc, "part_acc", torch.float32)
+            _need(part_ml, "part_ml", torch.float32)
+            if part_acc.numel() < n_seqs * num_heads * n_splits * v_dim or part_ml.numel() < n_seqs * num_heads * n_splits * 2:
+                raise KernelError("attention_decode: scratch is too small for this batch and split count")
+        _attention_latent(q, k_cache, out, block_table, None, None, seq_len, n_seqs, 1, page_tokens, scale, v_dim, n_splits, part_acc, part_ml)
+        return
+    if impl == "latent":
+        raise KernelError("the tensor-core kernel for cached latent rows does not take this call")
     if impl == "mma" and _special_mask(k_cache, v_cache, chunk):
         raise KernelError("the block-tile decode kernel takes no mask in chunks and no value heads shared by several key heads")
     extended = _extended_choice(q, k_cache, v_cache, page_tokens, ring_tokens, scale, penalty, keep_first, sink, v_dim, chunk, impl, "ws")

@@ -128,7 +128,13 @@ class LatentAttention:
     def cache_request(self):
         return KVRequest(1, self.row, None, shared_values=True)
 
-    def _splits(self, ctx) -> int:
+    def _splits(self, ctx, page_tokens: int) -> int:
+        """Key ranges per sequence of a one-token step.  The tensor-core kernel runs one block per SM, each with up to 64
+        heads of a sequence; the generic kernel four heads a block, several blocks per SM."""
+        if kernels.attention_latent_shape(self.runtime.dtype, self.row, self.rank, page_tokens) and self.scale > 0:
+            blocks = ctx.n_seqs * -(-self.heads // 64)
+            most = max(1, min(ctx.max_context // _MIN_KEYS_PER_SPLIT, _MAX_SPLIT_PAIRS // ctx.n_seqs, 32))
+            return max(1, min(most, self.runtime.sm_count // max(blocks, 1)))
         blocks = ctx.n_seqs * -(-self.heads // 4)
         most = max(1, min(ctx.max_context // _MIN_KEYS_PER_SPLIT, _MAX_SPLIT_PAIRS // ctx.n_seqs, 32))
         return max(1, min(most, (2 * self.runtime.sm_count) // max(blocks, 1)))
@@ -152,7 +158,7 @@ class LatentAttention:
         out = ws.view("latent.ctx", tokens, self.heads, self.rank)
         if ctx.is_decode:
             kernels.attention_decode(q, cache.k, cache.k, out, table, ctx.seq_len, 1, cache.page_tokens, cache.ring_tokens, None, self.scale,
-                                     self._splits(ctx), ws.view("attn.part_acc", _MAX_SPLIT_PAIRS * self.heads * self.rank),
+                                     self._splits(ctx, cache.page_tokens), ws.view("attn.part_acc", _MAX_SPLIT_PAIRS * self.heads * self.rank),
                                      ws.view("attn.part_ml", _MAX_SPLIT_PAIRS * self.heads * 2), v_dim=self.rank)
         else:
             kernels.attention_prefill(q, cache.k, cache.k, out, table, ctx.seq_start, ctx.seq_past, ctx.max_q_len, 1, cache.page_tokens,

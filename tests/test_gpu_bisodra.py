@@ -421,10 +421,14 @@ def test_a_product_per_head(dtype, tokens, heads, n, k, gated):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads, rank, rot_dim", [(3, 40, 8), (1, 132, 6), (6, 128, 16), (5, 8, 4), (2, 260, 24), (16, 512, 64)])
+@pytest.mark.parametrize("heads, rank, rot_dim", [(3, 40, 8), (1, 132, 6), (6, 128, 16), (5, 8, 4), (2, 260, 24), (16, 512, 64),
+                                                   (7, 56, 8), (4, 64, 24), (40, 96, 16), (70, 32, 16), (3, 264, 8)])
 def test_attention_over_latent_rows(dtype, heads, rank, rot_dim):
     """Every head's query [rank | rot_dim] against the one cached row per token, whose first ``rank`` elements are the
-    values: a prompt, a later portion and single tokens.  One far row carries the softmax of the last queries."""
+    values: a prompt, a later portion and single tokens.  One far row carries the softmax of the last queries.  In
+    bfloat16 the sizes that are multiples of 8 run on the tensor cores (rows padded to 16, head counts that do not divide a
+    tile of 64 rows, more heads than a tile has rows, a value size that the two warps of a row group share unevenly), the
+    others and float in the generic kernels."""
     torch.manual_seed(rank)
     store = STORE[dtype]
     total, prompt = 200, 190
