@@ -50,24 +50,29 @@ __device__ __forceinline__ void copy_page(uint32_t dst, const __nv_bfloat16* src
     }
 }
 
-template <int NT_MAX>                  // n8 tiles of value columns a warp may hold
+// NT_MAX: n8 tiles of value columns a warp may hold.  KP: parts into which the keys of a page are cut among the row
+// groups (1, 2 or 4).  With KP > 1 a block has 4 / KP row groups (16 or 32 rows, the heads of a one-token step) and row
+// group r of part k walks keys 64 k / KP .. of every page with a softmax of its own; a part's result is one more
+// partial result for the combine kernel: n_splits * KP per row, this block's at split * KP + k.
+template <int NT_MAX, int KP>
 __global__ void __launch_bounds__(LT_THREADS, 1) latent_attention_kernel(const LatentParams p) {
+    constexpr int GROUPS = 4 / KP, BLOCK_ROWS = 16 * GROUPS, SNT = 8 / KP, KEYS = PAGE / KP;
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int row = p.row, rank = p.rank, heads = p.heads;
     const int ksteps = (row + 15) >> 4, lds = ksteps * 16 + PAD;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int rg = warp >> 1, cg = warp & 1;
+    const int rg = (warp >> 1) % GROUPS, kpart = (warp >> 1) / GROUPS, cg = warp & 1, kb = kpart * KEYS;
     const int seq = blockIdx.z, split = blockIdx.y;
     const bool one_token = p.seq_len != nullptr;
     const int q_begin = one_token ? seq : p.seq_start[seq];
     const int q_len = one_token ? 1 : p.seq_start[seq + 1] - q_begin;
     const int past = one_token ? p.seq_len[seq] - 1 : p.seq_past[seq];
     const int total = q_len * heads;                       // (token, head) pairs of this sequence
-    const int q0 = blockIdx.x * LT_ROWS;
+    const int q0 = blockIdx.x * BLOCK_ROWS;
     if (q0 >= total) return;
-    const int rows = min(LT_ROWS, total - q0);
+    const int rows = min(BLOCK_ROWS, total - q0);
     const int* table = p.block_table + (size_t)seq * p.max_blocks;
     const int p_last = past + (q0 + rows - 1) / heads;     // below 0: a padded row of a captured step, which sees nothing
 
@@ -112,41 +117,41 @@ __global__ void __launch_bounds__(LT_THREADS, 1) latent_attention_kernel(const L
     const int warp_pos_min = past + min(q0 + rg * 16, last_row) / heads, warp_pos_max = past + min(q0 + rg * 16 + 15, last_row) / heads;
     const uint32_t q_frag = q_s + (uint32_t)((rg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * lds + (lane >> 4) * 8) * 2u;
     const int mi = lane >> 3;
-    const uint32_t k_frag = (uint32_t)(((mi >> 1) * 8 + (lane & 7)) * lds + (mi & 1) * 8) * 2u;
-    const uint32_t v_frag = (uint32_t)(((mi & 1) * 8 + (lane & 7)) * lds + pair0 * 16 + (mi >> 1) * 8) * 2u;
+    const uint32_t k_frag = (uint32_t)((kb + (mi >> 1) * 8 + (lane & 7)) * lds + (mi & 1) * 8) * 2u;
+    const uint32_t v_frag = (uint32_t)((kb + (mi & 1) * 8 + (lane & 7)) * lds + pair0 * 16 + (mi >> 1) * 8) * 2u;
 
     for (int tile = tile_begin; tile < tile_end; ++tile) {
         issue(tile + 1);
         cp_async_wait<1>();
         __syncthreads();
         const uint32_t k_s = kv0 + (uint32_t)((tile - tile_begin) & 1) * tile_bytes;
-        const int pos0 = tile * PAGE;
+        const int pos0 = tile * PAGE + kb;                         // position of this warp's first key of the page
         if (active && pos0 <= warp_pos_max) {
-            float s[8][4];
+            float s[SNT][4];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+            for (int i = 0; i < SNT; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
 #pragma unroll 2
             for (int ks = 0; ks < ksteps; ++ks) {
                 uint32_t a[4];
                 ldmatrix_x4(a, q_frag + (uint32_t)ks * 32u);
 #pragma unroll
-                for (int np = 0; np < 4; ++np) {
+                for (int np = 0; np < SNT / 2; ++np) {
                     uint32_t b[4];
                     ldmatrix_x4(b, k_s + k_frag + (uint32_t)(np * 16 * lds + ks * 16) * 2u);
                     mma_bf16(s[2 * np], a, b[0], b[1]);
                     mma_bf16(s[2 * np + 1], a, b[2], b[3]);
                 }
             }
-            if (pos0 + PAGE - 1 > warp_pos_min) {
+            if (pos0 + KEYS - 1 > warp_pos_min) {
 #pragma unroll
-                for (int nt = 0; nt < 8; ++nt)
+                for (int nt = 0; nt < SNT; ++nt)
 #pragma unroll
                     for (int e = 0; e < 4; ++e)
                         if (pos0 + nt * 8 + 2 * t + (e & 1) > qpos[e >> 1]) s[nt][e] = -INFINITY;
             }
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt)
+            for (int nt = 0; nt < SNT; ++nt)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
             float alpha[2];
@@ -160,7 +165,7 @@ __global__ void __launch_bounds__(LT_THREADS, 1) latent_attention_kernel(const L
                 m[r] = m_new;
                 float sum = 0.f;
 #pragma unroll
-                for (int nt = 0; nt < 8; ++nt) {
+                for (int nt = 0; nt < SNT; ++nt) {
                     s[nt][2 * r] = fast_exp2(fmaf(s[nt][2 * r], scale2, -m_use));
                     s[nt][2 * r + 1] = fast_exp2(fmaf(s[nt][2 * r + 1], scale2, -m_use));
                     sum += s[nt][2 * r] + s[nt][2 * r + 1];
@@ -170,7 +175,7 @@ __global__ void __launch_bounds__(LT_THREADS, 1) latent_attention_kernel(const L
 #pragma unroll
             for (int nt = 0; nt < NT_MAX; ++nt) { o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0]; o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1]; }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {                            // 16 keys at a time
+            for (int j = 0; j < SNT / 2; ++j) {                      // 16 keys at a time
                 const uint32_t pa[4] = {pack_bf16(s[2 * j][0], s[2 * j][1]), pack_bf16(s[2 * j][2], s[2 * j][3]),
                                         pack_bf16(s[2 * j + 1][0], s[2 * j + 1][1]), pack_bf16(s[2 * j + 1][2], s[2 * j + 1][3])};
 #pragma unroll
@@ -195,7 +200,7 @@ __global__ void __launch_bounds__(LT_THREADS, 1) latent_attention_kernel(const L
         const int local = rg * 16 + g + 8 * r;
         if (local >= rows) continue;
         const size_t pair = (size_t)q_begin * heads + q0 + local;      // (token, head) pair of the step
-        if (p.n_splits == 1) {
+        if (p.n_splits * KP == 1) {
             const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
             __nv_bfloat16* dst = p.out + pair * rank;
 #pragma unroll
@@ -204,7 +209,7 @@ __global__ void __launch_bounds__(LT_THREADS, 1) latent_attention_kernel(const L
                 if (nt < 2 * npairs && col < rank) *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(o[nt][2 * r] * inv, o[nt][2 * r + 1] * inv);
             }
         } else {
-            const size_t slot = pair * p.n_splits + split;
+            const size_t slot = pair * (p.n_splits * KP) + split * KP + kpart;
             float* dst = p.part_acc + slot * rank;
 #pragma unroll
             for (int nt = 0; nt < NT_MAX; ++nt) {
@@ -239,25 +244,36 @@ extern "C" int qt_attention_latent(const void* q, const void* cache, void* out, 
     QT_REQUIRE(scale > 0.f, "attention_latent: the score scale must be positive (the row maximum is taken before scaling)");
     QT_REQUIRE((seq_len != nullptr) != (seq_start != nullptr && seq_past != nullptr), "attention_latent: either seq_len or seq_start and seq_past");
     QT_REQUIRE(n_splits >= 1 && n_splits <= 65535 && (n_splits == 1 || (part_acc && part_ml)), "attention_latent: %d key ranges need scratch memory", n_splits);
+    // A one-token step of few heads leaves most row groups of a block without rows: there the keys of a page are cut
+    // among the row groups, and a block delivers 4 (up to 16 heads) or 2 (up to 32) of the n_splits partial results.
+    const int kp = !seq_len ? 1 : (heads <= 16 && n_splits % 4 == 0) ? 4 : (heads <= 32 && n_splits % 2 == 0) ? 2 : 1;
+    const int block_rows = 64 / kp;
     const int lds = (row + 15) / 16 * 16 + PAD;
     const size_t smem = (size_t)3 * PAGE * lds * 2;
     QT_REQUIRE(smem <= 227 * 1024, "attention_latent: rows of %d elements do not fit shared memory (use the generic kernel)", row);
     LatentParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, block_table, max_blocks, seq_start, seq_past,
-                   seq_len, heads, row, rank, scale, n_splits, part_acc, part_ml};
+                   seq_len, heads, row, rank, scale, n_splits / kp, part_acc, part_ml};
     const long long most_rows = (long long)(seq_len ? 1 : max_q_len) * heads;
-    dim3 grid((unsigned)((most_rows + LT_ROWS - 1) / LT_ROWS), n_splits, n_seqs);
+    dim3 grid((unsigned)((most_rows + block_rows - 1) / block_rows), n_splits / kp, n_seqs);
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
-#define QT_LAUNCH_LATENT(NT)                                                                                              \
+#define QT_LAUNCH_LATENT_KP(NT, KP)                                                                                       \
     do {                                                                                                                 \
         static bool ok = false;                                                                                          \
-        if (!ok) { rc = raise_smem(latent_attention_kernel<NT>, 227 * 1024, "attention_latent"); if (rc) return rc; ok = true; } \
-        launch_kernel(latent_attention_kernel<NT>, grid, dim3(LT_THREADS), smem, s, p);                                   \
+        if (!ok) { rc = raise_smem(latent_attention_kernel<NT, KP>, 227 * 1024, "attention_latent"); if (rc) return rc; ok = true; } \
+        launch_kernel(latent_attention_kernel<NT, KP>, grid, dim3(LT_THREADS), smem, s, p);                               \
+    } while (0)
+#define QT_LAUNCH_LATENT(NT)                                                                                              \
+    do {                                                                                                                 \
+        if (kp == 4) QT_LAUNCH_LATENT_KP(NT, 4);                                                                         \
+        else if (kp == 2) QT_LAUNCH_LATENT_KP(NT, 2);                                                                    \
+        else QT_LAUNCH_LATENT_KP(NT, 1);                                                                                 \
     } while (0)
     if (rank <= 128) QT_LAUNCH_LATENT(8);
     else if (rank <= 256) QT_LAUNCH_LATENT(16);
     else QT_LAUNCH_LATENT(32);
 #undef QT_LAUNCH_LATENT
+#undef QT_LAUNCH_LATENT_KP
     QT_CHECK_LAUNCH("attention_latent");
     if (n_splits > 1) {
         launch_kernel(attention_combine_mma_kernel, dim3(n_seqs * heads), dim3(128), 0, s, part_acc, part_ml, (__nv_bfloat16*)out, n_splits, rank, 0);

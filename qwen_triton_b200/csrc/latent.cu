@@ -13,9 +13,10 @@
 // latent_query_rot_kernel the rotated part of every head's query: rotation by position into the query rows.
 // head_product_kernel     Y[t, h, n] = sum_k X[t, h, k] W[h, n, k] for every head with its own matrix (float sums), with
 //                         strides for X and Y and optionally times sigmoid(gate[t, h * N + n]).
+// head_product_mma_kernel the same on the tensor cores (mma.sync m16n8k16) for bfloat16 matrices and results.
 // Rotation: element i of the rotated part turns with element i + rd / 2 by the angle whose cos and sin the table row
 // of the position holds (cos | sin, rd columns); elements beyond the first rd pass unchanged.
-#include "common.cuh"
+#include "attention_mma.cuh"
 
 #include <math.h>
 
@@ -225,6 +226,107 @@ __global__ void __launch_bounds__(256) head_product_kernel(const HeadProductPara
     }
 }
 
+// The same product on the tensor cores: bfloat16 matrices and results, X bfloat16 (copied by cp.async) or float partial
+// sums (added and rounded to bfloat16 on the way into shared memory).  grid (n tiles, token tiles, heads); four warps
+// form a tile of 64 tokens x 64 outputs (16 tokens a warp), K in slices of 64 through a two-stage ring.
+constexpr int HM_T = 64, HM_N = 64, HM_K = 64, HM_LDS = HM_K + 8;
+
+template <typename TI>
+__global__ void __launch_bounds__(128) head_product_mma_kernel(const HeadProductParams p) {
+    using namespace qt_mma;
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ __align__(16) __nv_bfloat16 tiles[2][2][HM_T * HM_LDS];      // [stage][X | W]
+    const int h = blockIdx.z, t0 = blockIdx.y * HM_T, n0 = blockIdx.x * HM_N;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const TI* x = (const TI*)p.x;
+    const __nv_bfloat16* w = (const __nv_bfloat16*)p.w + (size_t)h * p.n * p.k;
+    const int slices = (p.k + HM_K - 1) / HM_K;
+    auto issue = [&](int slice) {
+        if (slice < slices) {
+            const int k0 = slice * HM_K;
+            __nv_bfloat16* xs = tiles[slice & 1][0];
+            __nv_bfloat16* wt = tiles[slice & 1][1];
+            for (int i = tid; i < HM_T * (HM_K / 8); i += 128) {
+                const int r = i >> 3, c = (i & 7) * 8;
+                const int tok = t0 + r, k = k0 + c;
+                __nv_bfloat16* dst = xs + r * HM_LDS + c;
+                if (tok < p.n_tokens && k < p.k) {
+                    const size_t at = (size_t)((long long)tok * p.x_row + (long long)h * p.x_head + p.x_offset + k);
+                    if constexpr (sizeof(TI) == 2) {
+                        cp_async16(smem_u32(dst), x + at);
+                    } else {
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            packed[e] = pack_bf16(load_sum(x, at + 2 * e, p.x_splits, p.x_split_stride), load_sum(x, at + 2 * e + 1, p.x_splits, p.x_split_stride));
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    }
+                } else {
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+                }
+                const int n = n0 + r;
+                dst = wt + r * HM_LDS + c;
+                if (n < p.n && k < p.k) cp_async16(smem_u32(dst), w + (size_t)n * p.k + k);
+                else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        cp_async_commit();
+    };
+    issue(0);
+    float acc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+    const uint32_t a_off = (uint32_t)((warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * HM_LDS + (lane >> 4) * 8) * 2u;
+    const int mi = lane >> 3;
+    const uint32_t b_off = (uint32_t)(((mi >> 1) * 8 + (lane & 7)) * HM_LDS + (mi & 1) * 8) * 2u;
+    for (int slice = 0; slice < slices; ++slice) {
+        issue(slice + 1);
+        cp_async_wait<1>();
+        __syncthreads();
+        const uint32_t xs = smem_u32(tiles[slice & 1][0]), wt = smem_u32(tiles[slice & 1][1]);
+#pragma unroll
+        for (int ks = 0; ks < HM_K / 16; ++ks) {
+            uint32_t a[4];
+            ldmatrix_x4(a, xs + a_off + (uint32_t)ks * 32u);
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                uint32_t b[4];
+                ldmatrix_x4(b, wt + b_off + (uint32_t)(np * 16 * HM_LDS + ks * 16) * 2u);
+                mma_bf16(acc[2 * np], a, b[0], b[1]);
+                mma_bf16(acc[2 * np + 1], a, b[2], b[3]);
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    __nv_bfloat16* y = (__nv_bfloat16*)p.y;
+    const bool paired = ((p.y_row | p.y_head | (long long)p.y_offset) & 1) == 0;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int tok = t0 + warp * 16 + g + 8 * r;
+        if (tok >= p.n_tokens) continue;
+        __nv_bfloat16* dst = y + (size_t)((long long)tok * p.y_row + (long long)h * p.y_head + p.y_offset);
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            const int n = n0 + nt * 8 + 2 * t;
+            if (n >= p.n) continue;
+            float v0 = acc[nt][2 * r], v1 = acc[nt][2 * r + 1];
+            if (p.gate) {
+                const size_t at = (size_t)tok * p.gate_cols + p.gate_offset + (size_t)h * p.n + n;
+                v0 = v0 / (1.f + expf(-sum_splits(p.gate, at, p.gate_splits, p.gate_split_stride)));
+                if (n + 1 < p.n) v1 = v1 / (1.f + expf(-sum_splits(p.gate, at + 1, p.gate_splits, p.gate_split_stride)));
+            }
+            if (paired && n + 1 < p.n) {
+                *reinterpret_cast<uint32_t*>(dst + n) = pack_bf16(v0, v1);
+            } else {
+                dst[n] = __float2bfloat16_rn(v0);
+                if (n + 1 < p.n) dst[n + 1] = __float2bfloat16_rn(v1);
+            }
+        }
+    }
+}
+
 extern "C" int qt_head_product(const void* x, int x_dtype, int x_splits, long long x_split_stride, long long x_row, long long x_head, int x_offset,
                                const void* w, int w_dtype, void* y, int y_dtype, long long y_row, long long y_head, int y_offset,
                                const float* gate, int gate_splits, long long gate_split_stride, int gate_cols, int gate_offset,
@@ -237,6 +339,16 @@ extern "C" int qt_head_product(const void* x, int x_dtype, int x_splits, long lo
     HeadProductParams p{x, x_splits, (size_t)x_split_stride, x_row, x_head, x_offset, w, y, y_row, y_head, y_offset,
                         gate, gate_splits, (size_t)gate_split_stride, gate_cols, gate_offset, n_tokens, heads, n, k};
     dim3 grid((n + HP_TN - 1) / HP_TN, (n_tokens + HP_TM - 1) / HP_TM, heads);
+    // bfloat16 matrices and results whose rows start on 16 bytes take the tensor cores (QT_B200_HEAD_PRODUCT_MMA=0: never)
+    static const bool mma_allowed = [] { const char* env = getenv("QT_B200_HEAD_PRODUCT_MMA"); return !(env && env[0] == '0'); }();
+    if (mma_allowed && w_dtype == QT_BF16 && y_dtype == QT_BF16 && k % 8 == 0 && (n_tokens + HM_T - 1) / HM_T <= 65535 &&
+        (x_dtype == QT_F32 || (x_dtype == QT_BF16 && x_splits == 1 && x_row % 8 == 0 && x_head % 8 == 0 && x_offset % 8 == 0))) {
+        dim3 tiles((n + HM_N - 1) / HM_N, (n_tokens + HM_T - 1) / HM_T, heads);
+        if (x_dtype == QT_F32) launch_kernel(head_product_mma_kernel<float>, tiles, dim3(128), 0, s, p);
+        else launch_kernel(head_product_mma_kernel<__nv_bfloat16>, tiles, dim3(128), 0, s, p);
+        QT_CHECK_LAUNCH("head_product_mma");
+        return QT_OK;
+    }
 #define QT_LAUNCH_HP(TI, TW, TO) launch_kernel(head_product_kernel<TI, TW, TO>, grid, dim3(256), 0, s, p)
     if (x_dtype == QT_F32 && w_dtype == QT_F32 && y_dtype == QT_F32) QT_LAUNCH_HP(float, float, float);
     else if (x_dtype == QT_F32 && w_dtype == QT_BF16 && y_dtype == QT_BF16) QT_LAUNCH_HP(float, __nv_bfloat16, __nv_bfloat16);

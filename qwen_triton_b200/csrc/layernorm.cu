@@ -64,6 +64,90 @@ __global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __r
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<TO>((row[i] - mean) * inv * weight[i]);
 }
 
+// The same, four elements a thread at a time (16-byte loads of the sums and the stream, 8- or 16-byte stores), for rows
+// whose length and strides are multiples of four.  Every element is summed over the splits in the same order as above.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename TD, typename TO>
+__global__ void add_layernorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_splits, size_t split_stride,
+                                         const float* __restrict__ post_weight, const float* __restrict__ weight, float eps,
+                                         TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float4 row4[];          // [hidden / 4]
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* res = residual + (size_t)src * hidden;
+    const float inv_n = 1.f / (float)hidden;
+    const int quads = hidden >> 2;
+    if (delta) {
+        float sum = 0.f;
+        for (int i = threadIdx.x; i < quads; i += blockDim.x) {
+            const TD* at = delta + (size_t)src * hidden + 4 * i;
+            float4 d = load4(at);
+            for (int s = 1; s < n_splits; ++s) {
+                const float4 e = load4(at + (size_t)s * split_stride);
+                d.x += e.x; d.y += e.y; d.z += e.z; d.w += e.w;
+            }
+            row4[i] = d;
+            sum += (d.x + d.y) + (d.z + d.w);
+        }
+        if (post_weight) {
+            const float mean = block_sum(sum, scratch) * inv_n;
+            float sq = 0.f;
+            for (int i = threadIdx.x; i < quads; i += blockDim.x) {
+                const float4 d = row4[i];
+                const float a = d.x - mean, b = d.y - mean, c = d.z - mean, e = d.w - mean;
+                sq += (a * a + b * b) + (c * c + e * e);
+            }
+            const float inv = rsqrtf(block_sum(sq, scratch) * inv_n + eps);
+            for (int i = threadIdx.x; i < quads; i += blockDim.x) {
+                const float4 d = row4[i], w = load4(post_weight + 4 * i);
+                row4[i] = make_float4((d.x - mean) * inv * w.x, (d.y - mean) * inv * w.y, (d.z - mean) * inv * w.z, (d.w - mean) * inv * w.w);
+            }
+        }
+    }
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < quads; i += blockDim.x) {
+        float4 x = load4(res + 4 * i);
+        if (delta) {
+            const float4 d = row4[i];
+            x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
+        }
+        row4[i] = x;
+        if (!rows) store4(res + 4 * i, x);
+        sum += (x.x + x.y) + (x.z + x.w);
+    }
+    const float mean = block_sum(sum, scratch) * inv_n;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < quads; i += blockDim.x) {
+        const float4 d = row4[i];
+        const float a = d.x - mean, b = d.y - mean, c = d.z - mean, e = d.w - mean;
+        sq += (a * a + b * b) + (c * c + e * e);
+    }
+    const float inv = rsqrtf(block_sum(sq, scratch) * inv_n + eps);
+    TO* o = out + (size_t)r * hidden;
+    for (int i = threadIdx.x; i < quads; i += blockDim.x) {
+        const float4 d = row4[i], w = load4(weight + 4 * i);
+        store4(o + 4 * i, make_float4((d.x - mean) * inv * w.x, (d.y - mean) * inv * w.y, (d.z - mean) * inv * w.z, (d.w - mean) * inv * w.w));
+    }
+}
+
 extern "C" int qt_add_layernorm(float* residual, const void* delta, int delta_dtype, int n_splits, long long split_stride,
                                 const float* post_weight, const float* weight, float eps, void* out, int out_dtype, const int* rows,
                                 int n_rows, int hidden, void* stream) {
@@ -76,14 +160,22 @@ extern "C" int qt_add_layernorm(float* residual, const void* delta, int delta_dt
     cudaStream_t s = (cudaStream_t)stream;
     int threads = ((hidden + 3) / 4 + 31) / 32 * 32;
     threads = threads < 64 ? 64 : threads > 1024 ? 1024 : threads;
+    // rows of whole quads whose every pointer and stride keeps 16-byte (8-byte for bfloat16) alignment go four elements a thread
+    const auto misaligned = [](const void* ptr) { return ((uintptr_t)ptr & 15) != 0; };
+    const bool vec = hidden % 4 == 0 && split_stride % 4 == 0 && !misaligned(residual) && !misaligned(delta) && !misaligned(post_weight) &&
+                     !misaligned(weight) && !misaligned(out);
 #define QT_LAUNCH_LN(TD, TO)                                                                                                        \
     do {                                                                                                                            \
         if (smem > 48 * 1024) {                                                                                                     \
             cudaError_t err = cudaFuncSetAttribute(add_layernorm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
             if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "add_layernorm: cannot raise shared memory: %s", cudaGetErrorString(err)); \
         }                                                                                                                           \
-        launch_kernel(add_layernorm_kernel<TD, TO>, dim3(n_rows), dim3(threads), smem, s, residual, (const TD*)delta, n_splits,     \
-                      (size_t)split_stride, post_weight, weight, eps, (TO*)out, rows, hidden);                                      \
+        if (vec && smem <= 48 * 1024)                                                                                               \
+            launch_kernel(add_layernorm_vec_kernel<TD, TO>, dim3(n_rows), dim3(threads), smem, s, residual, (const TD*)delta, n_splits, \
+                          (size_t)split_stride, post_weight, weight, eps, (TO*)out, rows, hidden);                                  \
+        else                                                                                                                        \
+            launch_kernel(add_layernorm_kernel<TD, TO>, dim3(n_rows), dim3(threads), smem, s, residual, (const TD*)delta, n_splits, \
+                          (size_t)split_stride, post_weight, weight, eps, (TO*)out, rows, hidden);                                  \
     } while (0)
     if (delta_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_LN(float, float);
     else if (delta_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_LN(float, __nv_bfloat16);

@@ -129,12 +129,17 @@ class LatentAttention:
         return KVRequest(1, self.row, None, shared_values=True)
 
     def _splits(self, ctx, page_tokens: int) -> int:
-        """Key ranges per sequence of a one-token step.  The tensor-core kernel runs one block per SM, each with up to 64
-        heads of a sequence; the generic kernel four heads a block, several blocks per SM."""
+        """Partial results per (sequence, head) of a one-token step.  The tensor-core kernel runs one block per SM, each
+        with up to 64 heads of a sequence and a range of its pages; with at most 16 (32) heads a block cuts the keys of
+        every page into 4 (2) parts, each a partial result of its own.  The generic kernel runs four heads a block,
+        several blocks per SM."""
         if kernels.attention_latent_shape(self.runtime.dtype, self.row, self.rank, page_tokens) and self.scale > 0:
+            parts = 4 if self.heads <= 16 else 2 if self.heads <= 32 else 1
+            if parts * ctx.n_seqs > _MAX_SPLIT_PAIRS:
+                parts = 1
             blocks = ctx.n_seqs * -(-self.heads // 64)
-            most = max(1, min(ctx.max_context // _MIN_KEYS_PER_SPLIT, _MAX_SPLIT_PAIRS // ctx.n_seqs, 32))
-            return max(1, min(most, self.runtime.sm_count // max(blocks, 1)))
+            most = max(1, min(ctx.max_context // _MIN_KEYS_PER_SPLIT, _MAX_SPLIT_PAIRS // (ctx.n_seqs * parts), 32))
+            return parts * max(1, min(most, self.runtime.sm_count // max(blocks, 1)))
         blocks = ctx.n_seqs * -(-self.heads // 4)
         most = max(1, min(ctx.max_context // _MIN_KEYS_PER_SPLIT, _MAX_SPLIT_PAIRS // ctx.n_seqs, 32))
         return max(1, min(most, (2 * self.runtime.sm_count) // max(blocks, 1)))

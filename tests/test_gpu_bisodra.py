@@ -100,7 +100,7 @@ def as_int(values):
 
 
 # ----------------------------------------------------------------------------- each mechanism alone
-@pytest.mark.parametrize("width, rows", [(96, 5), (130, 33), (7, 1), (1024, 3)])
+@pytest.mark.parametrize("width, rows", [(96, 5), (130, 33), (7, 1), (1024, 3), (5000, 2), (2052, 4)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_layer_norm_before_and_after_a_sublayer(width, rows, out_dtype):
     """stream += norm_b(delta), then norm_a(stream): both with the mean taken off, a weight and no bias.  Rows with a
@@ -453,12 +453,15 @@ def test_attention_over_latent_rows(dtype, heads, rank, rot_dim):
     kernels.attention_prefill(q[120:prompt].to(DEV, store), pool, pool, out, table, as_int([0, prompt - 120]), as_int([120]), prompt - 120, 1, PAGE,
                               0, None, scale, v_dim=rank)
     close(out, want[120:prompt], dtype, "portion")
-    for t in range(prompt, total):
-        for splits in (1, 3):
+    # single tokens late and early in the sequence (fewer keys than a page, than a part of a page, one more than a page),
+    # with partial results that a block delivers one, two or four at a time
+    for t in list(range(prompt, total)) + [0, 4, 16, 39, 63, 64]:
+        for splits in (1, 3) if prompt < t < total - 1 else (1, 2, 3, 4, 8):
             out = torch.full((1, heads, rank), float("nan"), dtype=store, device=DEV)
             kernels.attention_decode(q[t:t + 1].to(DEV, store), pool, pool, out, table, as_int([t + 1]), 1, PAGE, 0, None, scale, splits,
-                                     torch.empty(4 * heads * rank, device=DEV), torch.empty(8 * heads, device=DEV), v_dim=rank)
-            close(out, want[t:t + 1], dtype, f"token {t}, {splits} ranges")
+                                     torch.full((8 * heads * rank,), float("nan"), device=DEV), torch.full((16 * heads,), float("nan"), device=DEV),
+                                     v_dim=rank)
+            close(out, want[t:t + 1], dtype, f"token {t}, {splits} partial results")
     kernels.check_status(DEV)
 
 
