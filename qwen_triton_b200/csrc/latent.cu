@@ -251,24 +251,39 @@ __global__ void __launch_bounds__(128) head_product_mma_kernel(const HeadProduct
                 const int r = i >> 3, c = (i & 7) * 8;
                 const int tok = t0 + r, k = k0 + c;
                 __nv_bfloat16* dst = xs + r * HM_LDS + c;
-                if (tok < p.n_tokens && k < p.k) {
-                    const size_t at = (size_t)((long long)tok * p.x_row + (long long)h * p.x_head + p.x_offset + k);
-                    if constexpr (sizeof(TI) == 2) {
-                        cp_async16(smem_u32(dst), x + at);
-                    } else {
-                        uint32_t packed[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            packed[e] = pack_bf16(load_sum(x, at + 2 * e, p.x_splits, p.x_split_stride), load_sum(x, at + 2 * e + 1, p.x_splits, p.x_split_stride));
-                        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                    }
-                } else {
-                    *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+                if constexpr (sizeof(TI) == 2) {
+                    if (tok < p.n_tokens && k < p.k) cp_async16(smem_u32(dst), x + (size_t)((long long)tok * p.x_row + (long long)h * p.x_head + p.x_offset + k));
+                    else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
                 }
                 const int n = n0 + r;
                 dst = wt + r * HM_LDS + c;
                 if (n < p.n && k < p.k) cp_async16(smem_u32(dst), w + (size_t)n * p.k + k);
                 else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            }
+            if constexpr (sizeof(TI) == 4) {
+                // float partial sums: every load of the slice is issued before the first value is rounded and stored
+                constexpr int PER = HM_T * (HM_K / 8) / 128;
+                float4 lo[PER], hi[PER];
+#pragma unroll
+                for (int j = 0; j < PER; ++j) {
+                    const int i = tid + j * 128, tok = t0 + (i >> 3), k = k0 + (i & 7) * 8;
+                    lo[j] = hi[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (tok < p.n_tokens && k < p.k) {
+                        const float* at = (const float*)p.x + (size_t)((long long)tok * p.x_row + (long long)h * p.x_head + p.x_offset + k);
+                        for (int sp = 0; sp < p.x_splits; ++sp) {
+                            const float4 a = __ldg(reinterpret_cast<const float4*>(at + (size_t)sp * p.x_split_stride));
+                            const float4 b = __ldg(reinterpret_cast<const float4*>(at + (size_t)sp * p.x_split_stride) + 1);
+                            lo[j].x += a.x; lo[j].y += a.y; lo[j].z += a.z; lo[j].w += a.w;
+                            hi[j].x += b.x; hi[j].y += b.y; hi[j].z += b.z; hi[j].w += b.w;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < PER; ++j) {
+                    const int i = tid + j * 128;
+                    *reinterpret_cast<uint4*>(xs + (i >> 3) * HM_LDS + (i & 7) * 8) =
+                        make_uint4(pack_bf16(lo[j].x, lo[j].y), pack_bf16(lo[j].z, lo[j].w), pack_bf16(hi[j].x, hi[j].y), pack_bf16(hi[j].z, hi[j].w));
+                }
             }
         }
         cp_async_commit();
@@ -302,6 +317,31 @@ __global__ void __launch_bounds__(128) head_product_mma_kernel(const HeadProduct
     cp_async_wait<0>();
     __nv_bfloat16* y = (__nv_bfloat16*)p.y;
     const bool paired = ((p.y_row | p.y_head | (long long)p.y_offset) & 1) == 0;
+    if (p.gate) {
+        // the gates of all of this thread's results are summed (split by split, the loads of a split independent of one
+        // another) before the first result is stored
+        float gates[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) gates[nt][0] = gates[nt][1] = gates[nt][2] = gates[nt][3] = 0.f;
+        for (int sp = 0; sp < p.gate_splits; ++sp) {
+            const float* gate = p.gate + (size_t)sp * p.gate_split_stride;
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int tok = t0 + warp * 16 + g + 8 * r;
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt) {
+                    const int n = n0 + nt * 8 + 2 * t;
+                    const size_t at = (size_t)tok * p.gate_cols + p.gate_offset + (size_t)h * p.n + n;
+                    if (tok < p.n_tokens && n < p.n) gates[nt][2 * r] += __ldg(gate + at);
+                    if (tok < p.n_tokens && n + 1 < p.n) gates[nt][2 * r + 1] += __ldg(gate + at + 1);
+                }
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[nt][e] = acc[nt][e] / (1.f + expf(-gates[nt][e]));
+    }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int tok = t0 + warp * 16 + g + 8 * r;
@@ -311,12 +351,7 @@ __global__ void __launch_bounds__(128) head_product_mma_kernel(const HeadProduct
         for (int nt = 0; nt < 8; ++nt) {
             const int n = n0 + nt * 8 + 2 * t;
             if (n >= p.n) continue;
-            float v0 = acc[nt][2 * r], v1 = acc[nt][2 * r + 1];
-            if (p.gate) {
-                const size_t at = (size_t)tok * p.gate_cols + p.gate_offset + (size_t)h * p.n + n;
-                v0 = v0 / (1.f + expf(-sum_splits(p.gate, at, p.gate_splits, p.gate_split_stride)));
-                if (n + 1 < p.n) v1 = v1 / (1.f + expf(-sum_splits(p.gate, at + 1, p.gate_splits, p.gate_split_stride)));
-            }
+            const float v0 = acc[nt][2 * r], v1 = acc[nt][2 * r + 1];
             if (paired && n + 1 < p.n) {
                 *reinterpret_cast<uint32_t*>(dst + n) = pack_bf16(v0, v1);
             } else {
@@ -342,7 +377,9 @@ extern "C" int qt_head_product(const void* x, int x_dtype, int x_splits, long lo
     // bfloat16 matrices and results whose rows start on 16 bytes take the tensor cores (QT_B200_HEAD_PRODUCT_MMA=0: never)
     static const bool mma_allowed = [] { const char* env = getenv("QT_B200_HEAD_PRODUCT_MMA"); return !(env && env[0] == '0'); }();
     if (mma_allowed && w_dtype == QT_BF16 && y_dtype == QT_BF16 && k % 8 == 0 && (n_tokens + HM_T - 1) / HM_T <= 65535 &&
-        (x_dtype == QT_F32 || (x_dtype == QT_BF16 && x_splits == 1 && x_row % 8 == 0 && x_head % 8 == 0 && x_offset % 8 == 0))) {
+        ((x_dtype == QT_F32 && x_row % 4 == 0 && x_head % 4 == 0 && x_offset % 4 == 0 && x_split_stride % 4 == 0 && ((uintptr_t)x & 15) == 0) ||
+         (x_dtype == QT_BF16 && x_splits == 1 && x_row % 8 == 0 && x_head % 8 == 0 && x_offset % 8 == 0 && ((uintptr_t)x & 15) == 0)) &&
+        ((uintptr_t)w & 15) == 0) {
         dim3 tiles((n + HM_N - 1) / HM_N, (n_tokens + HM_T - 1) / HM_T, heads);
         if (x_dtype == QT_F32) launch_kernel(head_product_mma_kernel<float>, tiles, dim3(128), 0, s, p);
         else launch_kernel(head_product_mma_kernel<__nv_bfloat16>, tiles, dim3(128), 0, s, p);

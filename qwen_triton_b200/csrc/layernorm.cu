@@ -64,8 +64,10 @@ __global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __r
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<TO>((row[i] - mean) * inv * weight[i]);
 }
 
-// The same, four elements a thread at a time (16-byte loads of the sums and the stream, 8- or 16-byte stores), for rows
-// whose length and strides are multiples of four.  Every element is summed over the splits in the same order as above.
+// The same for rows of up to 4,096 elements whose length and strides are multiples of four: a thread holds four elements
+// of the row in registers (16-byte loads of the sums and the stream, all issued before the first sum is needed; 8- or
+// 16-byte stores), and the row never passes through shared memory.  Every element is summed over the splits in the same
+// order as above.
 __device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
     const uint2 raw = *reinterpret_cast<const uint2*>(p);
@@ -88,64 +90,40 @@ __global__ void add_layernorm_vec_kernel(float* __restrict__ residual, const TD*
                                          TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ float4 row4[];          // [hidden / 4]
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* res = residual + (size_t)src * hidden;
     const float inv_n = 1.f / (float)hidden;
-    const int quads = hidden >> 2;
-    if (delta) {
-        float sum = 0.f;
-        for (int i = threadIdx.x; i < quads; i += blockDim.x) {
+    const int i = threadIdx.x;
+    const bool has = i < (hidden >> 2);              // a thread holds one quad of the row in registers (blockDim.x >= hidden / 4)
+    // everything the thread reads is asked for at once: the sums, the stream and both weights
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f), d = x, w = x, pw = x;
+    if (has) {
+        x = load4(res + 4 * i);
+        w = load4(weight + 4 * i);
+        if (post_weight) pw = load4(post_weight + 4 * i);
+        if (delta) {
             const TD* at = delta + (size_t)src * hidden + 4 * i;
-            float4 d = load4(at);
+            d = load4(at);
             for (int s = 1; s < n_splits; ++s) {
                 const float4 e = load4(at + (size_t)s * split_stride);
                 d.x += e.x; d.y += e.y; d.z += e.z; d.w += e.w;
             }
-            row4[i] = d;
-            sum += (d.x + d.y) + (d.z + d.w);
-        }
-        if (post_weight) {
-            const float mean = block_sum(sum, scratch) * inv_n;
-            float sq = 0.f;
-            for (int i = threadIdx.x; i < quads; i += blockDim.x) {
-                const float4 d = row4[i];
-                const float a = d.x - mean, b = d.y - mean, c = d.z - mean, e = d.w - mean;
-                sq += (a * a + b * b) + (c * c + e * e);
-            }
-            const float inv = rsqrtf(block_sum(sq, scratch) * inv_n + eps);
-            for (int i = threadIdx.x; i < quads; i += blockDim.x) {
-                const float4 d = row4[i], w = load4(post_weight + 4 * i);
-                row4[i] = make_float4((d.x - mean) * inv * w.x, (d.y - mean) * inv * w.y, (d.z - mean) * inv * w.z, (d.w - mean) * inv * w.w);
-            }
         }
     }
-    float sum = 0.f;
-    for (int i = threadIdx.x; i < quads; i += blockDim.x) {
-        float4 x = load4(res + 4 * i);
-        if (delta) {
-            const float4 d = row4[i];
-            x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
-        }
-        row4[i] = x;
-        if (!rows) store4(res + 4 * i, x);
-        sum += (x.x + x.y) + (x.z + x.w);
-    }
-    const float mean = block_sum(sum, scratch) * inv_n;
-    float sq = 0.f;
-    for (int i = threadIdx.x; i < quads; i += blockDim.x) {
-        const float4 d = row4[i];
+    if (delta && post_weight) {
+        const float mean = block_sum((d.x + d.y) + (d.z + d.w), scratch) * inv_n;
         const float a = d.x - mean, b = d.y - mean, c = d.z - mean, e = d.w - mean;
-        sq += (a * a + b * b) + (c * c + e * e);
+        const float inv = rsqrtf(block_sum(has ? (a * a + b * b) + (c * c + e * e) : 0.f, scratch) * inv_n + eps);
+        d = make_float4(a * inv * pw.x, b * inv * pw.y, c * inv * pw.z, e * inv * pw.w);
     }
-    const float inv = rsqrtf(block_sum(sq, scratch) * inv_n + eps);
-    TO* o = out + (size_t)r * hidden;
-    for (int i = threadIdx.x; i < quads; i += blockDim.x) {
-        const float4 d = row4[i], w = load4(weight + 4 * i);
-        store4(o + 4 * i, make_float4((d.x - mean) * inv * w.x, (d.y - mean) * inv * w.y, (d.z - mean) * inv * w.z, (d.w - mean) * inv * w.w));
-    }
+    if (delta) { x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w; }
+    if (!rows && has) store4(res + 4 * i, x);
+    const float mean = block_sum((x.x + x.y) + (x.z + x.w), scratch) * inv_n;
+    const float a = x.x - mean, b = x.y - mean, c = x.z - mean, e = x.w - mean;
+    const float inv = rsqrtf(block_sum(has ? (a * a + b * b) + (c * c + e * e) : 0.f, scratch) * inv_n + eps);
+    if (has) store4(out + (size_t)r * hidden + 4 * i, make_float4(a * inv * w.x, b * inv * w.y, c * inv * w.z, e * inv * w.w));
 }
 
 extern "C" int qt_add_layernorm(float* residual, const void* delta, int delta_dtype, int n_splits, long long split_stride,
@@ -160,9 +138,9 @@ extern "C" int qt_add_layernorm(float* residual, const void* delta, int delta_dt
     cudaStream_t s = (cudaStream_t)stream;
     int threads = ((hidden + 3) / 4 + 31) / 32 * 32;
     threads = threads < 64 ? 64 : threads > 1024 ? 1024 : threads;
-    // rows of whole quads whose every pointer and stride keeps 16-byte (8-byte for bfloat16) alignment go four elements a thread
+    // rows of at most 1,024 whole quads whose every pointer and stride keeps 16-byte alignment go four elements a thread
     const auto misaligned = [](const void* ptr) { return ((uintptr_t)ptr & 15) != 0; };
-    const bool vec = hidden % 4 == 0 && split_stride % 4 == 0 && !misaligned(residual) && !misaligned(delta) && !misaligned(post_weight) &&
+    const bool vec = hidden % 4 == 0 && hidden <= 4 * threads && split_stride % 4 == 0 && !misaligned(residual) && !misaligned(delta) && !misaligned(post_weight) &&
                      !misaligned(weight) && !misaligned(out);
 #define QT_LAUNCH_LN(TD, TO)                                                                                                        \
     do {                                                                                                                            \
@@ -170,8 +148,8 @@ extern "C" int qt_add_layernorm(float* residual, const void* delta, int delta_dt
             cudaError_t err = cudaFuncSetAttribute(add_layernorm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
             if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "add_layernorm: cannot raise shared memory: %s", cudaGetErrorString(err)); \
         }                                                                                                                           \
-        if (vec && smem <= 48 * 1024)                                                                                               \
-            launch_kernel(add_layernorm_vec_kernel<TD, TO>, dim3(n_rows), dim3(threads), smem, s, residual, (const TD*)delta, n_splits, \
+        if (vec)                                                                                                                    \
+            launch_kernel(add_layernorm_vec_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, s, residual, (const TD*)delta, n_splits, \
                           (size_t)split_stride, post_weight, weight, eps, (TO*)out, rows, hidden);                                  \
         else                                                                                                                        \
             launch_kernel(add_layernorm_kernel<TD, TO>, dim3(n_rows), dim3(threads), smem, s, residual, (const TD*)delta, n_splits, \
@@ -196,6 +174,22 @@ __global__ void activation_kernel(const TI* __restrict__ in, int n_splits, size_
         out[i] = from_float<TO>(gate_activation<false>(load_sum(in, (size_t)i, n_splits, split_stride), act));
 }
 
+// Four elements a thread, for totals, strides and pointers that keep the alignment of a quad.
+template <typename TI, typename TO>
+__global__ void activation_vec_kernel(const TI* __restrict__ in, int n_splits, size_t split_stride, TO* __restrict__ out, long long quads, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += (long long)gridDim.x * blockDim.x) {
+        float4 v = load4(in + 4 * i);
+        for (int s = 1; s < n_splits; ++s) {
+            const float4 e = load4(in + 4 * i + (size_t)s * split_stride);
+            v.x += e.x; v.y += e.y; v.z += e.z; v.w += e.w;
+        }
+        store4(out + 4 * i, make_float4(gate_activation<false>(v.x, act), gate_activation<false>(v.y, act), gate_activation<false>(v.z, act),
+                                        gate_activation<false>(v.w, act)));
+    }
+}
+
 extern "C" int qt_activation(const void* in, int in_dtype, int n_splits, long long split_stride, void* out, int out_dtype, int n_rows,
                              int cols, int act, void* stream) {
     QT_REQUIRE(n_rows >= 0 && cols > 0 && n_splits >= 1, "activation: bad sizes rows=%d cols=%d splits=%d", n_rows, cols, n_splits);
@@ -205,8 +199,16 @@ extern "C" int qt_activation(const void* in, int in_dtype, int n_splits, long lo
     const long long total = (long long)n_rows * cols;
     long long blocks = (total + 255) / 256;
     if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
-#define QT_LAUNCH_ACT(TI, TO) \
-    launch_kernel(activation_kernel<TI, TO>, dim3((unsigned)blocks), dim3(256), 0, s, (const TI*)in, n_splits, (size_t)split_stride, (TO*)out, total, act)
+    const bool vec = total % 4 == 0 && split_stride % 4 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0;
+    if (vec) blocks = (total / 4 + 255) / 256;
+    if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
+#define QT_LAUNCH_ACT(TI, TO)                                                                                                        \
+    do {                                                                                                                             \
+        if (vec) launch_kernel(activation_vec_kernel<TI, TO>, dim3((unsigned)blocks), dim3(256), 0, s, (const TI*)in, n_splits,       \
+                               (size_t)split_stride, (TO*)out, total / 4, act);                                                      \
+        else launch_kernel(activation_kernel<TI, TO>, dim3((unsigned)blocks), dim3(256), 0, s, (const TI*)in, n_splits,              \
+                           (size_t)split_stride, (TO*)out, total, act);                                                              \
+    } while (0)
     if (in_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_ACT(float, float);
     else if (in_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_ACT(float, __nv_bfloat16);
     else if (in_dtype == QT_BF16 && out_dtype == QT_BF16) QT_LAUNCH_ACT(__nv_bfloat16, __nv_bfloat16);
