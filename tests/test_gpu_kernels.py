@@ -506,8 +506,8 @@ def test_sample_of_distinct_rows_with_top_k_and_top_p():
 def test_kernels_refuse_what_they_cannot_run():
     with pytest.raises(kernels.KernelError, match="CUDA tensor"):
         kernels.argmax(torch.zeros(1, 4), torch.zeros(1, dtype=torch.int32))
-    q = torch.zeros(1, 2, 272, device=DEV)
-    cache = torch.zeros(1, 1, PAGE, 272, device=DEV)
+    q = torch.zeros(1, 2, 648, device=DEV)
+    cache = torch.zeros(1, 1, PAGE, 648, device=DEV)
     with pytest.raises(kernels.KernelError, match="head_dim"):
         kernels.attention_decode(q, cache, cache, torch.empty_like(q), torch.zeros(1, 1, dtype=torch.int32, device=DEV),
                                  torch.ones(1, dtype=torch.int32, device=DEV), 1, PAGE, 0, None, 1.0, 1, None, None)
