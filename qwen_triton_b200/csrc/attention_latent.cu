@@ -6,12 +6,14 @@
 // 64 consecutive pairs of one sequence (64 / heads tokens of a prompt, or the heads of a one-token step) and walks the
 // pages of 64 tokens its rows can see through a two-stage cp.async ring, so a page is read once for all heads.
 //
-// Eight warps: warp w owns rows 16 (w / 2) .. + 15 and the value columns of half (w % 2).  Both warps of a row group
-// compute the row group's 16 x 64 scores (the query fragments come from shared memory by ldmatrix at every step of
-// the sum, a row being too long for registers) and keep the same online softmax, in float in the base-2 domain; each
-// multiplies the weights with its half of the value columns.  Nothing is exchanged between warps until the result is
-// written.  With `n_splits` > 1 the pages of a sequence are cut into that many ranges, one block each, whose partial
-// results go to float scratch and are merged by the combine kernel that the other decode kernels use.
+// Eight warps: warp w owns rows 16 (w / 2) .. + 15 and the value columns of half (w % 2).  The two warps of a row group
+// form the scores of 32 keys of the page each (the query fragments come from shared memory by ldmatrix at every step of
+// the sum, a row being too long for registers), hand each other the row maxima and then the weights through shared
+// memory (two barriers of 64 threads a page), keep the same online softmax, in float in the base-2 domain, and each
+// multiplies all 64 weights with its half of the value columns.  With `n_splits` > 1 the pages of a sequence are cut into
+// that many ranges, one block each, whose partial results go to float scratch and are merged by the combine kernel that
+// the other decode kernels use.  (Where a page's keys are cut among the row groups, see the kernel, both warps of a row
+// group still form the same scores.)
 //
 // Causal: the key at position j is visible to the query at position i iff j <= i.  Takes rows and ranks that are
 // multiples of 8 (shared-memory rows are padded with zeros to the next multiple of 16), ranks up to 512, a positive
@@ -120,13 +122,102 @@ __global__ void __launch_bounds__(LT_THREADS, 1) latent_attention_kernel(const L
     const uint32_t k_frag = (uint32_t)((kb + (mi >> 1) * 8 + (lane & 7)) * lds + (mi & 1) * 8) * 2u;
     const uint32_t v_frag = (uint32_t)((kb + (mi & 1) * 8 + (lane & 7)) * lds + pair0 * 16 + (mi >> 1) * 8) * 2u;
 
+    // KP == 1: what the two warps of a row group exchange.  xw[r]: the four floats of padding behind the query tile's row
+    // of this thread's row r (maxima of the two warps, then their sums); p_rows: the row group's 16 x 64 weights, bfloat16.
+    float* xw[2] = {reinterpret_cast<float*>(smem_raw + ((size_t)(rg * 16 + g) * lds + ksteps * 16) * 2),
+                    reinterpret_cast<float*>(smem_raw + ((size_t)(rg * 16 + g + 8) * lds + ksteps * 16) * 2)};
+    uint8_t* p_rows = smem_raw + 3 * (size_t)tile_bytes + (size_t)rg * 16 * PAGE * 2;
+    const uint32_t p_frag = smem_u32(p_rows) + (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * PAGE + (lane >> 4) * 8) * 2u;
+    auto pair_sync = [](int group) { asm volatile("bar.sync %0, 64;" ::"r"(group + 1) : "memory"); };
+
     for (int tile = tile_begin; tile < tile_end; ++tile) {
         issue(tile + 1);
         cp_async_wait<1>();
         __syncthreads();
         const uint32_t k_s = kv0 + (uint32_t)((tile - tile_begin) & 1) * tile_bytes;
         const int pos0 = tile * PAGE + kb;                         // position of this warp's first key of the page
-        if (active && pos0 <= warp_pos_max) {
+        if constexpr (KP == 1) {
+            // The two warps of a row group form the scores of 32 keys each and hand each other the row maxima (through
+            // the padding behind the rows of the query tile) and the weights (through p_s), so no score is formed twice.
+            if (active && pos0 <= warp_pos_max) {
+                const int kc = cg * 32;
+                float s[4][4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll 2
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    uint32_t a[4];
+                    ldmatrix_x4(a, q_frag + (uint32_t)ks * 32u);
+#pragma unroll
+                    for (int np = 0; np < 2; ++np) {
+                        uint32_t b[4];
+                        ldmatrix_x4(b, k_s + k_frag + (uint32_t)((kc + np * 16) * lds + ks * 16) * 2u);
+                        mma_bf16(s[2 * np], a, b[0], b[1]);
+                        mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+                    }
+                }
+                if (pos0 + PAGE - 1 > warp_pos_min) {
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (pos0 + kc + nt * 8 + 2 * t + (e & 1) > qpos[e >> 1]) s[nt][e] = -INFINITY;
+                }
+                float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                    if (t == 0) xw[r][cg] = mx[r];
+                }
+                pair_sync(rg);
+                float alpha[2];
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    mx[r] = fmaxf(mx[r], xw[r][cg ^ 1]);
+                    const float m_new = fmaxf(m[r], mx[r] * scale2);
+                    const float m_use = m_new == -INFINITY ? 0.f : m_new;
+                    alpha[r] = fast_exp2(m[r] - m_use);
+                    m[r] = m_new;
+                    float sum = 0.f;
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt) {
+                        s[nt][2 * r] = fast_exp2(fmaf(s[nt][2 * r], scale2, -m_use));
+                        s[nt][2 * r + 1] = fast_exp2(fmaf(s[nt][2 * r + 1], scale2, -m_use));
+                        sum += s[nt][2 * r] + s[nt][2 * r + 1];
+                        *reinterpret_cast<uint32_t*>(p_rows + ((g + 8 * r) * PAGE + kc + nt * 8 + 2 * t) * 2) = pack_bf16(s[nt][2 * r], s[nt][2 * r + 1]);
+                    }
+                    l[r] = l[r] * alpha[r] + sum;              // this warp's keys only; the halves meet after the last page
+                }
+                pair_sync(rg);
+#pragma unroll
+                for (int nt = 0; nt < NT_MAX; ++nt) { o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0]; o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1]; }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {                        // 16 keys at a time: two steps of its own, two of the other warp's
+                    uint32_t pa[4];
+                    if ((j >> 1) == cg) {
+                        const int jj = j & 1;
+                        pa[0] = pack_bf16(s[2 * jj][0], s[2 * jj][1]); pa[1] = pack_bf16(s[2 * jj][2], s[2 * jj][3]);
+                        pa[2] = pack_bf16(s[2 * jj + 1][0], s[2 * jj + 1][1]); pa[3] = pack_bf16(s[2 * jj + 1][2], s[2 * jj + 1][3]);
+                    } else {
+                        ldmatrix_x4(pa, p_frag + (uint32_t)j * 32u);
+                    }
+#pragma unroll
+                    for (int nt2 = 0; nt2 < NT_MAX / 2; ++nt2) {
+                        if (nt2 < npairs) {
+                            uint32_t b[4];
+                            ldmatrix_x4_trans(b, k_s + v_frag + (uint32_t)(j * 16 * lds + nt2 * 16) * 2u);
+                            mma_bf16(o[2 * nt2], pa, b[0], b[1]);
+                            mma_bf16(o[2 * nt2 + 1], pa, b[2], b[3]);
+                        }
+                    }
+                }
+            }
+        } else if (active && pos0 <= warp_pos_max) {
             float s[SNT][4];
 #pragma unroll
             for (int i = 0; i < SNT; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
@@ -197,6 +288,15 @@ __global__ void __launch_bounds__(LT_THREADS, 1) latent_attention_kernel(const L
     for (int r = 0; r < 2; ++r) {
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    if constexpr (KP == 1) {                                    // the two warps' sums over their halves of the keys meet
+        if (t == 0) { xw[0][2 + cg] = l[0]; xw[1][2 + cg] = l[1]; }
+        pair_sync(rg);
+        l[0] += xw[0][2 + (cg ^ 1)];
+        l[1] += xw[1][2 + (cg ^ 1)];
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
         const int local = rg * 16 + g + 8 * r;
         if (local >= rows) continue;
         const size_t pair = (size_t)q_begin * heads + q0 + local;      // (token, head) pair of the step
@@ -249,7 +349,7 @@ extern "C" int qt_attention_latent(const void* q, const void* cache, void* out, 
     const int kp = !seq_len ? 1 : (heads <= 16 && n_splits % 4 == 0) ? 4 : (heads <= 32 && n_splits % 2 == 0) ? 2 : 1;
     const int block_rows = 64 / kp;
     const int lds = (row + 15) / 16 * 16 + PAD;
-    const size_t smem = (size_t)3 * PAGE * lds * 2;
+    const size_t smem = (size_t)3 * PAGE * lds * 2 + (size_t)4 * 16 * PAGE * 2;      // three tiles and the row groups' weights
     QT_REQUIRE(smem <= 227 * 1024, "attention_latent: rows of %d elements do not fit shared memory (use the generic kernel)", row);
     LatentParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, block_table, max_blocks, seq_start, seq_past,
                    seq_len, heads, row, rank, scale, n_splits / kp, part_acc, part_ml};
