@@ -72,7 +72,8 @@ __global__ void __launch_bounds__(LT_THREADS, 1) latent_attention_kernel(const L
     const int q_len = one_token ? 1 : p.seq_start[seq + 1] - q_begin;
     const int past = one_token ? p.seq_len[seq] - 1 : p.seq_past[seq];
     const int total = q_len * heads;                       // (token, head) pairs of this sequence
-    const int q0 = blockIdx.x * BLOCK_ROWS;
+    // a prompt's tiles in descending order: the last rows see the most keys, and the blocks that walk the most pages start first
+    const int q0 = (one_token ? (int)blockIdx.x : (int)(gridDim.x - 1 - blockIdx.x)) * BLOCK_ROWS;
     if (q0 >= total) return;
     const int rows = min(BLOCK_ROWS, total - q0);
     const int* table = p.block_table + (size_t)seq * p.max_blocks;
