@@ -646,13 +646,24 @@ __global__ void attention_combine_mma_kernel(const float* __restrict__ part_acc,
                                              __nv_bfloat16* __restrict__ out, int n_splits, int d, int sink) {
     pdl_launch_dependents();
     pdl_wait();
+    constexpr int KEPT = 256;                                        // partial results whose factors the block keeps in shared memory
+    __shared__ float factors[KEPT];
     const size_t item = blockIdx.x;
+    const float* ml = part_ml + item * n_splits * 2;
     float m_all = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) m_all = fmaxf(m_all, part_ml[(item * n_splits + s) * 2]);
+    for (int s = 0; s < n_splits; ++s) m_all = fmaxf(m_all, ml[2 * s]);
+    const bool kept = n_splits <= KEPT;
+    if (kept) {                                                      // exp(m_s - m) once per partial result, not once per column
+        for (int s = threadIdx.x; s < n_splits; s += blockDim.x) {
+            const float ms = ml[2 * s];
+            factors[s] = ms == -INFINITY ? 0.f : __expf(ms - m_all);
+        }
+        __syncthreads();
+    }
     float l_all = 0.f;
     for (int s = 0; s < n_splits; ++s) {
-        const float ms = part_ml[(item * n_splits + s) * 2];
-        l_all += ms == -INFINITY ? 0.f : part_ml[(item * n_splits + s) * 2 + 1] * __expf(ms - m_all);
+        const float ms = ml[2 * s];
+        l_all += ms == -INFINITY ? 0.f : ml[2 * s + 1] * (kept ? factors[s] : __expf(ms - m_all));
     }
     float factor = 1.f;
     if (sink) {                                                      // the maxima are in the natural-log domain here
@@ -660,11 +671,20 @@ __global__ void attention_combine_mma_kernel(const float* __restrict__ part_acc,
         factor = __expf(m_all - top);
         l_all = l_all * factor + __expf(-top);
     }
+    const float* acc = part_acc + item * n_splits * d;
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float a = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float ms = part_ml[(item * n_splits + s) * 2];
-            if (ms != -INFINITY) a += part_acc[(item * n_splits + s) * d + c] * __expf(ms - m_all);
+        if (kept) {                                                  // the loads do not wait for one another; an empty range's
+#pragma unroll 8                                                     // sums are read and dropped
+            for (int s = 0; s < n_splits; ++s) {
+                const float v = acc[(size_t)s * d + c], f = factors[s];
+                a += f != 0.f ? v * f : 0.f;
+            }
+        } else {
+            for (int s = 0; s < n_splits; ++s) {
+                const float ms = ml[2 * s];
+                if (ms != -INFINITY) a += acc[(size_t)s * d + c] * __expf(ms - m_all);
+            }
         }
         out[item * d + c] = __float2bfloat16_rn(a * factor / l_all);
     }
