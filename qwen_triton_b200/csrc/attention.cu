@@ -10,7 +10,8 @@
 // have fewer heads than the key cache: `nv` value heads, key head g reading value head g % nv (several score maps
 // over one set of values).  With `r1` alone the penalty is linear, r1_h * (p - j).  With `keep_first` > 0 a windowed
 // query also sees the keys at positions below `keep_first`, at their true distances.  With `sink` the softmax has one
-// more term of score 0 that carries no value: p_j = exp(s_j) / (1 + sum exp(s_j)).  `v_row` is the length of a value
+// more term of score 0 that carries no value: p_j = exp(s_j) / (1 + sum exp(s_j)); with `sinks` (one float per query head) the
+// term's score is the head's number, taken as it is (not scaled).  `v_row` is the length of a value
 // row in the value cache where it is longer than `dv` (values that are the leading elements of the cached keys).
 //
 // Counterparts in luozoupi/Qwen-Triton: kernels/flash_attention.py:54-152 (one kernel for both
@@ -40,6 +41,7 @@ struct AttnParams {
     int keep_first;       // > 0 with a window: keys at positions below this stay visible
     int sink;             // 1: one more softmax term of score 0 without a value
     int v_row;            // elements between the value rows of neighbouring tokens (dv unless the rows are longer)
+    const float* sinks;   // [nq] the sink term's score per query head (null: 0)
 };
 
 // r2 < 0 marks the linear form r1 * distance
@@ -49,10 +51,10 @@ __device__ __forceinline__ float distance_penalty(float r1, float r2, int distan
 
 // Result of a softmax row with a sink term of score 0: the factor on the accumulator and the denominator, from the
 // running maximum m and sum l (both relative to m).  Formed around max(m, 0) so that neither exponential overflows.
-__device__ __forceinline__ void with_sink(float m, float& l, float& factor) {
-    const float top = fmaxf(m, 0.f);
+__device__ __forceinline__ void with_sink(float m, float& l, float& factor, float sink = 0.f) {
+    const float top = fmaxf(m, sink);
     factor = expf(m - top);
-    l = l * factor + expf(-top);
+    l = l * factor + expf(sink - top);
 }
 
 // ----------------------------------------------------------------------------- many tokens per sequence
@@ -166,7 +168,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(const 
         const int r = warp + i * PF_WARPS;
         if (r >= rows) continue;
         float factor = 1.f;
-        if (p.sink) with_sink(m[i], l[i], factor);
+        if (p.sink) with_sink(m[i], l[i], factor, p.sinks ? p.sinks[head] : 0.f);
         const float inv = factor / l[i];
 #pragma unroll
         for (int j = 0; j < DMAX / 32; ++j) {
@@ -209,7 +211,7 @@ extern "C" int qt_attention_prefill(const void* q, const void* k_cache, const vo
                                     const int* block_table, int max_blocks, const int* seq_start, const int* seq_past,
                                     int n_seqs, int max_q_len, int nq, int nkv, int d, int page_tokens, int ring_tokens,
                                     int window, float scale, int dv, const float* r1, const float* r2, int chunk, int nv,
-                                    int keep_first, int sink, int v_row, void* stream) {
+                                    int keep_first, int sink, int v_row, const float* sinks, void* stream) {
     if (n_seqs == 0 || max_q_len == 0) return QT_OK;
     if (nv <= 0) nv = nkv;
     if (v_row <= 0) v_row = dv;
@@ -217,7 +219,7 @@ extern "C" int qt_attention_prefill(const void* q, const void* k_cache, const vo
     if (rc) return rc;
     QT_REQUIRE(nq <= 65535 && n_seqs <= 65535, "attention_prefill: too many heads or sequences for one launch");
     AttnParams p{q, k_cache, v_cache, out, block_table, max_blocks, seq_start, seq_past, n_seqs, nq, nkv, d, page_tokens, ring_tokens, window, scale,
-                 dv, r1, r2, chunk, nv, keep_first, sink, v_row};
+                 dv, r1, r2, chunk, nv, keep_first, sink, v_row, sinks};
     cudaStream_t s = (cudaStream_t)stream;
     return QT_DISPATCH_DTYPE(dtype, "attention_prefill", {
         if (dv <= 64) return launch_prefill<T, 64>(p, max_q_len, s);
@@ -373,7 +375,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
         const int head = head_base + h;
         if (dp.n_splits == 1) {
             float factor = 1.f;
-            if (p.sink) with_sink(m_all, l_all, factor);
+            if (p.sink) with_sink(m_all, l_all, factor, p.sinks ? p.sinks[head] : 0.f);
             ((T*)p.out)[((size_t)seq * p.nq + head) * dv + c] = from_float<T>(a_all * factor / l_all);
         } else {
             const size_t slot = ((size_t)seq * p.nq + head) * dp.n_splits + split;
@@ -386,7 +388,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
 // One block per (sequence, head): out = sum_s acc_s e^{m_s - m} / sum_s l_s e^{m_s - m}; empty splits have m = -inf.
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                         T* __restrict__ out, int n_splits, int d, int sink) {
+                                         T* __restrict__ out, int n_splits, int d, int sink, const float* __restrict__ sinks, int nq) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t item = blockIdx.x;   // seq * nq + head
@@ -398,7 +400,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc, con
         l_all += ms == -INFINITY ? 0.f : part_ml[(item * n_splits + s) * 2 + 1] * expf(ms - m_all);
     }
     float factor = 1.f;
-    if (sink) with_sink(m_all, l_all, factor);
+    if (sink) with_sink(m_all, l_all, factor, sinks ? sinks[item % nq] : 0.f);
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float a = 0.f;
         for (int s = 0; s < n_splits; ++s) {
@@ -424,7 +426,7 @@ static int launch_decode_heads(const DecodeParams& dp, cudaStream_t stream) {
     launch_kernel(attention_decode_kernel<T, DMAX, DEC_HEADS>, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, dp);
     QT_CHECK_LAUNCH("attention_decode");
     if (dp.n_splits > 1) {
-        launch_kernel(attention_combine_kernel<T>, dim3(p.n_seqs * p.nq), dim3(128), 0, stream, dp.part_acc, dp.part_ml, (T*)p.out, dp.n_splits, p.dv, p.sink);
+        launch_kernel(attention_combine_kernel<T>, dim3(p.n_seqs * p.nq), dim3(128), 0, stream, dp.part_acc, dp.part_ml, (T*)p.out, dp.n_splits, p.dv, p.sink, p.sinks, p.nq);
         QT_CHECK_LAUNCH("attention_combine");
     }
     return QT_OK;
@@ -445,7 +447,7 @@ extern "C" int qt_attention_decode(const void* q, const void* k_cache, const voi
                                    const int* block_table, int max_blocks, const int* seq_len, int n_seqs, int nq,
                                    int nkv, int d, int page_tokens, int ring_tokens, int window, float scale,
                                    int n_splits, float* part_acc, float* part_ml, int dv, const float* r1, const float* r2,
-                                   int chunk, int nv, int keep_first, int sink, int v_row, void* stream) {
+                                   int chunk, int nv, int keep_first, int sink, int v_row, const float* sinks, void* stream) {
     if (n_seqs == 0) return QT_OK;
     if (nv <= 0) nv = nkv;
     if (v_row <= 0) v_row = dv;
@@ -455,7 +457,7 @@ extern "C" int qt_attention_decode(const void* q, const void* k_cache, const voi
     QT_REQUIRE(n_splits == 1 || (part_acc && part_ml), "attention_decode: split results need scratch memory");
     QT_REQUIRE(n_seqs <= 65535, "attention_decode: too many sequences for one launch");
     DecodeParams dp{{q, k_cache, v_cache, out, block_table, max_blocks, nullptr, nullptr, n_seqs, nq, nkv, d, page_tokens, ring_tokens, window, scale,
-                     dv, r1, r2, chunk, nv, keep_first, sink, v_row},
+                     dv, r1, r2, chunk, nv, keep_first, sink, v_row, sinks},
                     seq_len, n_splits, part_acc, part_ml};
     cudaStream_t s = (cudaStream_t)stream;
     return QT_DISPATCH_DTYPE(dtype, "attention_decode", {

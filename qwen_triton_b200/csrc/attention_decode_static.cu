@@ -84,7 +84,7 @@ extern "C" int qt_attention_decode_static(const void* q, const void* k_cache, co
     QT_CHECK_LAUNCH("attention_decode_static");
     if (n_splits > 1) {
         launch_kernel(attention_combine_mma_kernel, dim3(n_seqs * nq), dim3(128), 0, s, (const float*)part_acc, (const float*)part_ml,
-                      (__nv_bfloat16*)out, n_splits, d, 0);
+                      (__nv_bfloat16*)out, n_splits, d, 0, (const float*)nullptr, 1);
         QT_CHECK_LAUNCH("attention_decode_static (merge)");
     }
     return QT_OK;

@@ -377,7 +377,7 @@ extern "C" int qt_attention_latent(const void* q, const void* cache, void* out, 
 #undef QT_LAUNCH_LATENT_KP
     QT_CHECK_LAUNCH("attention_latent");
     if (n_splits > 1) {
-        launch_kernel(attention_combine_mma_kernel, dim3(n_seqs * heads), dim3(128), 0, s, part_acc, part_ml, (__nv_bfloat16*)out, n_splits, rank, 0);
+        launch_kernel(attention_combine_mma_kernel, dim3(n_seqs * heads), dim3(128), 0, s, part_acc, part_ml, (__nv_bfloat16*)out, n_splits, rank, 0, (const float*)nullptr, 1);
         QT_CHECK_LAUNCH("attention_combine_mma");
     }
     return QT_OK;

@@ -85,7 +85,7 @@ extern "C" int qt_attention_decode_mma(const void* q, const void* k_cache, const
     }
     QT_CHECK_LAUNCH("attention_decode_mma");
     if (n_splits > 1) {
-        launch_kernel(attention_combine_mma_kernel, dim3(n_seqs * nq), dim3(128), 0, s, part_acc, part_ml, (__nv_bfloat16*)out, n_splits, d, 0);
+        launch_kernel(attention_combine_mma_kernel, dim3(n_seqs * nq), dim3(128), 0, s, part_acc, part_ml, (__nv_bfloat16*)out, n_splits, d, 0, (const float*)nullptr, 1);
         QT_CHECK_LAUNCH("attention_combine_mma");
     }
     return QT_OK;
@@ -98,7 +98,7 @@ extern "C" int qt_attention_decode_ws(const void* q, const void* k_cache, const 
                                       const int* block_table, int max_blocks, const int* seq_len, int n_seqs, int nq,
                                       int nkv, int d, int page_tokens, int ring_tokens, int window, float scale,
                                       int n_splits, int warps, float* part_acc, float* part_ml, const float* r1, const float* r2,
-                                      int chunk, int nv, int keep_first, int sink, void* stream) {
+                                      int chunk, int nv, int keep_first, int sink, const float* sinks, void* stream) {
     QT_REQUIRE(chunk >= 0 && nv >= 0 && (nv == 0 || nkv % nv == 0), "attention_decode_ws: chunk=%d, %d value heads for %d key heads", chunk, nv, nkv);
     if (n_seqs == 0) return QT_OK;
     int rc = check("attention_decode_ws", n_seqs, nq, nkv, d, page_tokens, ring_tokens, window);
@@ -121,7 +121,7 @@ extern "C" int qt_attention_decode_ws(const void* q, const void* k_cache, const 
     QT_REQUIRE(n_splits == 1 || cluster || (part_acc && part_ml), "attention_decode_ws: split results need scratch memory");
     MmaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out,
                 block_table, max_blocks, nullptr, nullptr, seq_len, n_seqs, nq, nkv, d, ring_tokens, window, scale,
-                n_splits, part_acc, part_ml, 2, cluster ? 1 : 0, r1, r2, chunk, nv, keep_first, sink};
+                n_splits, part_acc, part_ml, 2, cluster ? 1 : 0, r1, r2, chunk, nv, keep_first, sink, sinks};
     const size_t smem = rings + (cluster ? inboxes : 0);
     dim3 grid(n_splits, nkv * ((group + 15) / 16), n_seqs), block(32 * warps);
     cudaStream_t s = (cudaStream_t)stream;
@@ -144,7 +144,7 @@ extern "C" int qt_attention_decode_ws(const void* q, const void* k_cache, const 
 #undef QT_LAUNCH_WS
     QT_CHECK_LAUNCH("attention_decode_ws");
     if (n_splits > 1 && !cluster) {
-        launch_kernel(attention_combine_mma_kernel, dim3(n_seqs * nq), dim3(128), 0, s, part_acc, part_ml, (__nv_bfloat16*)out, n_splits, d, sink);
+        launch_kernel(attention_combine_mma_kernel, dim3(n_seqs * nq), dim3(128), 0, s, part_acc, part_ml, (__nv_bfloat16*)out, n_splits, d, sink, sinks, nq);
         QT_CHECK_LAUNCH("attention_combine_mma");
     }
     return QT_OK;
@@ -154,7 +154,7 @@ extern "C" int qt_attention_prefill_mma(const void* q, const void* k_cache, cons
                                         const int* block_table, int max_blocks, const int* seq_start, const int* seq_past,
                                         int n_seqs, int max_q_len, int nq, int nkv, int d, int page_tokens, int ring_tokens,
                                         int window, float scale, const float* r1, const float* r2, int chunk, int nv, int keep_first,
-                                        int sink, void* stream) {
+                                        int sink, const float* sinks, void* stream) {
     QT_REQUIRE(chunk >= 0 && nv >= 0 && (nv == 0 || nkv % nv == 0), "attention_prefill_mma: chunk=%d, %d value heads for %d key heads", chunk, nv, nkv);
     if (n_seqs == 0 || max_q_len == 0) return QT_OK;
     int rc = check("attention_prefill_mma", n_seqs, nq, nkv, d, page_tokens, ring_tokens, window);
@@ -165,7 +165,7 @@ extern "C" int qt_attention_prefill_mma(const void* q, const void* k_cache, cons
     QT_REQUIRE(r1 == nullptr || scale > 0.f, "attention_prefill_mma: with a distance penalty the score scale must be positive");
     MmaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out,
                 block_table, max_blocks, seq_start, seq_past, nullptr, n_seqs, nq, nkv, d, ring_tokens, window, scale,
-                1, nullptr, nullptr, 2, 0, r1, r2, chunk, nv, keep_first, sink};
+                1, nullptr, nullptr, 2, 0, r1, r2, chunk, nv, keep_first, sink, sinks};
     const int lds = d + PAD;
     const size_t smem = (size_t)4 * PAGE * lds * 2;
     dim3 grid((max_q_len + PF_BQ - 1) / PF_BQ, nq, n_seqs);

@@ -59,14 +59,17 @@ struct MmaParams {
     int keep_first = 0;
     // sink: the softmax has one more term of score 0 that carries no value, p_j = e^{s_j} / (1 + sum e^{s_j}).
     int sink = 0;
+    // sinks: the sink term's score per query head, taken as it is (not scaled); null: 0.
+    const float* sinks = nullptr;
 };
 
 // The factor on a row's accumulator and its new denominator when the sink term joins a softmax whose running maximum
 // (scaled, base 2) is m and whose sum relative to m is l; formed around max(m, 0) so that no exponential overflows.
-__device__ __forceinline__ void join_sink(float m, float& l, float& factor) {
-    const float top = fmaxf(m, 0.f);
+__device__ __forceinline__ void join_sink(float m, float& l, float& factor, float sink = 0.f) {
+    const float s2 = sink * 1.4426950408889634f;
+    const float top = fmaxf(m, s2);
     factor = exp2f(m - top);
-    l = l * factor + exp2f(-top);
+    l = l * factor + exp2f(s2 - top);
 }
 
 __device__ __forceinline__ int chunk_start(int pos, int chunk) { return chunk > 0 ? pos / chunk * chunk : 0; }
@@ -605,7 +608,7 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
         const int head = head_base + r;
         if (gridDim.x == 1) {
             float factor = 1.f;
-            if (p.sink) join_sink(m_all, l_all, factor);
+            if (p.sink) join_sink(m_all, l_all, factor, p.sinks ? p.sinks[head] : 0.f);
             p.out[((size_t)seq * p.nq + head) * d + c] = __float2bfloat16_rn(a_all * factor / l_all);
         } else if (p.cluster_merge) {
             float* slot = inbox + (size_t)split * inbox_stride;
@@ -634,7 +637,7 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
                     a_all += slot[i] * f;
                 }
                 float factor = 1.f;
-                if (p.sink) join_sink(m_all, l_all, factor);
+                if (p.sink) join_sink(m_all, l_all, factor, p.sinks ? p.sinks[head_base + r] : 0.f);
                 p.out[((size_t)seq * p.nq + head_base + r) * d + (i % d)] = __float2bfloat16_rn(a_all * factor / l_all);
             }
         }
@@ -643,7 +646,8 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
 
 // One block per (sequence, head): out = sum_s acc_s e^{m_s - m} / sum_s l_s e^{m_s - m}; empty splits have m = -inf.
 __global__ void attention_combine_mma_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                             __nv_bfloat16* __restrict__ out, int n_splits, int d, int sink) {
+                                             __nv_bfloat16* __restrict__ out, int n_splits, int d, int sink,
+                                             const float* __restrict__ sinks, int nq) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int KEPT = 256;                                        // partial results whose factors the block keeps in shared memory
@@ -667,9 +671,10 @@ __global__ void attention_combine_mma_kernel(const float* __restrict__ part_acc,
     }
     float factor = 1.f;
     if (sink) {                                                      // the maxima are in the natural-log domain here
-        const float top = fmaxf(m_all, 0.f);
+        const float score = sinks ? sinks[item % nq] : 0.f;
+        const float top = fmaxf(m_all, score);
         factor = __expf(m_all - top);
-        l_all = l_all * factor + __expf(-top);
+        l_all = l_all * factor + __expf(score - top);
     }
     const float* acc = part_acc + item * n_splits * d;
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
@@ -871,7 +876,7 @@ __global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const Mma
         const int row = warp * 16 + g + 8 * r;
         if (row < rows) {
             float factor = 1.f;
-            if (p.sink) join_sink(m[r], l[r], factor);
+            if (p.sink) join_sink(m[r], l[r], factor, p.sinks ? p.sinks[head] : 0.f);
             const float inv = factor / l[r];
             __nv_bfloat16* dst = p.out + ((size_t)(q_begin + q0 + row) * p.nq + head) * d;
 #pragma unroll

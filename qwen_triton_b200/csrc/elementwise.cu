@@ -385,7 +385,32 @@ struct QkvParams {
     int n_tokens, nq, nkv, d, page_tokens, ring_tokens, write_kv, kv_in_proj;
     int interleaved;        // rotation pairs are (2i, 2i + 1) instead of (i, i + rd/2)
     int nv, dv;             // value heads and their size (the keys' unless given)
+    int unit_norm;          // q and k heads are divided by their root mean square without a weight
+    const float* row_inv;   // [T, 2]: q and k are normed over the whole row of heads with these factors (q_weight [nq d], k_weight [nkv d])
+    int extra_cols;         // columns of the projection behind q, k and v that this kernel leaves alone
 };
+
+// The factors of a norm over the whole projection: row_inv[t] = {rsqrt(mean(q_t^2) + eps), rsqrt(mean(k_t^2) + eps)} over all
+// nq d (nkv d) elements of token t at once.  One block per token.
+template <typename TI>
+__global__ void qk_row_rms_kernel(const TI* __restrict__ qkv, int n_splits, size_t split_stride, size_t cols, int q_cols, int k_cols, float eps,
+                                  float* __restrict__ row_inv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < q_cols + k_cols; i += blockDim.x) {
+        const float x = load_sum(qkv, (size_t)t * cols + i, n_splits, split_stride);
+        if (i < q_cols) sq += x * x; else sk += x * x;
+    }
+    sq = block_sum(sq, scratch);
+    sk = block_sum(sk, scratch);
+    if (threadIdx.x == 0) {
+        row_inv[2 * t] = rsqrtf(sq / (float)q_cols + eps);
+        row_inv[2 * t + 1] = k_cols > 0 ? rsqrtf(sk / (float)k_cols + eps) : 0.f;
+    }
+}
 
 template <typename TI, typename TO, bool VEC>
 __global__ void qk_norm_rope_write_kernel(const QkvParams p) {
@@ -403,7 +428,7 @@ __global__ void qk_norm_rope_write_kernel(const QkvParams p) {
     if (!is_q && !is_k && (p.nv != p.nkv || p.dv != p.d)) {
         // a value head of its own size: summed, stored
         const int vh = head - p.nq - p.nkv;
-        const size_t cols = (size_t)(p.nq + p.nkv) * p.d + (size_t)p.nv * p.dv;
+        const size_t cols = (size_t)(p.nq + p.nkv) * p.d + (size_t)p.nv * p.dv + (size_t)p.extra_cols;
         const size_t from = (size_t)t * cols + (size_t)(p.nq + p.nkv) * p.d + (size_t)vh * p.dv;
         const int* table = p.block_table + (size_t)p.token_seq[t] * p.max_blocks;
         TO* dst = (TO*)p.v_cache + cache_offset(table, p.token_pos[t], p.ring_tokens, p.page_tokens, p.nv, vh, p.dv);
@@ -419,9 +444,14 @@ __global__ void qk_norm_rope_write_kernel(const QkvParams p) {
         return;
     }
     float* vec = smem + warp * p.d;
-    const size_t in_base = (size_t)t * ((size_t)p.nq * p.d + (p.kv_in_proj ? (size_t)p.nkv * p.d + (size_t)p.nv * p.dv : 0)) + (size_t)head * p.d;
+    const size_t in_base = (size_t)t * ((size_t)p.nq * p.d + (p.kv_in_proj ? (size_t)p.nkv * p.d + (size_t)p.nv * p.dv : 0) + (size_t)p.extra_cols) +
+                           (size_t)head * p.d;
     const TI* in = (const TI*)p.qkv;
     const float* w = is_q ? p.q_weight : (is_k ? p.k_weight : nullptr);
+    if (w && p.row_inv) w += (size_t)(is_q ? head : head - p.nq) * p.d;        // a weight over the whole row of heads
+    // a rotation leaves a head's sum of squares as it is, so a norm without a weight that follows the rotation has the
+    // factor of the sums as they come, and, both being linear, norm and rotation may change places
+    const bool normed = (is_q || is_k) && (w || p.unit_norm || p.row_inv);
 
     // 1. the head's vector in float (split-K partials added up), its sum of squares
     float sq = 0.f;
@@ -441,7 +471,7 @@ __global__ void qk_norm_rope_write_kernel(const QkvParams p) {
     }
     // 2. RMSNorm over the head (q and k heads with a weight)
     float inv = 1.f;
-    if (w) inv = rsqrtf(warp_sum(sq) / (float)p.d + p.eps);
+    if (normed) inv = p.row_inv ? p.row_inv[2 * t + (is_q ? 0 : 1)] : rsqrtf(warp_sum(sq) / (float)p.d + p.eps);
     __syncwarp();
 
     TO* dst;
@@ -457,7 +487,7 @@ __global__ void qk_norm_rope_write_kernel(const QkvParams p) {
     const int half = p.rotary_dim >> 1;
     const bool rotate = (is_q || is_k) && half > 0;
     const float* cs = p.cos_sin + (size_t)(pos < p.max_pos ? pos : p.max_pos - 1) * p.rotary_dim;
-    auto value = [&](int i) { return w ? vec[i] * inv * w[i] : vec[i]; };
+    auto value = [&](int i) { return normed ? (w ? vec[i] * inv * w[i] : vec[i] * inv) : vec[i]; };
     auto rotated = [&](int i) {
         float y = value(i);
         if (rotate && i < p.rotary_dim) {
@@ -619,10 +649,13 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
                                      const int* token_pos, const int* block_table, int max_blocks,
                                      const float* q_weight, const float* k_weight, float eps, const float* cos_sin,
                                      int rotary_dim, int max_pos, int n_tokens, int nq, int nkv, int d, int page_tokens,
-                                     int ring_tokens, int write_kv, int kv_in_proj, int interleaved, int nv, int dv, void* stream) {
+                                     int ring_tokens, int write_kv, int kv_in_proj, int interleaved, int nv, int dv, int unit_norm, int whole_norm,
+                                     float* row_inv, int extra_cols, void* stream) {
     if (nv <= 0) nv = nkv;
     if (dv <= 0) dv = d;
     const bool own_values = nv != nkv || dv != d;
+    QT_REQUIRE(extra_cols >= 0 && (!whole_norm || (row_inv && q_weight && (k_weight || !kv_in_proj) && !unit_norm)),
+               "qk_norm_rope_write: a norm over the whole projection needs its factors' buffer and both weights");
     QT_REQUIRE(n_tokens >= 0 && nq > 0 && nkv > 0 && d > 0 && d <= 1024, "qk_norm_rope_write: bad sizes T=%d nq=%d nkv=%d d=%d", n_tokens, nq, nkv, d);
     QT_REQUIRE(rotary_dim >= 0 && rotary_dim <= d && rotary_dim % 2 == 0, "qk_norm_rope_write: rotary_dim=%d must be even and at most head_dim=%d", rotary_dim, d);
     QT_REQUIRE(rotary_dim == 0 || (cos_sin && max_pos > 0), "qk_norm_rope_write: rotation needs a cos/sin table");
@@ -631,7 +664,8 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
     QT_REQUIRE(!write_kv || kv_in_proj, "qk_norm_rope_write: nothing to write without k and v in the projection");
     if (n_tokens == 0) return QT_OK;
     QkvParams p{qkv, n_splits, (size_t)split_stride, q_out, k_cache, v_cache, token_seq, token_pos, block_table, max_blocks,
-                q_weight, k_weight, eps, cos_sin, rotary_dim, max_pos, n_tokens, nq, nkv, d, page_tokens, ring_tokens, write_kv, kv_in_proj, interleaved, nv, dv};
+                q_weight, k_weight, eps, cos_sin, rotary_dim, max_pos, n_tokens, nq, nkv, d, page_tokens, ring_tokens, write_kv, kv_in_proj, interleaved, nv, dv,
+                unit_norm, whole_norm ? row_inv : nullptr, extra_cols};
     const int warps = 4;
     const long long items = (long long)n_tokens * (nq + (kv_in_proj ? nkv + nv : 0));
     const unsigned grid = (unsigned)((items + warps - 1) / warps);
@@ -639,7 +673,18 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
     cudaStream_t s = (cudaStream_t)stream;
     // 16-byte loads and stores need head_dim % 8 == 0 (bfloat16 rows of the cache and of q) and aligned bases
     // (q and k heads of a projection whose values have their own shape take them too, if the values' columns keep the rows aligned)
-    const bool vec = (!own_values || (nv * dv) % 8 == 0) && d % 8 == 0 && split_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
+    if (whole_norm) {
+        const size_t cols = (size_t)nq * d + (kv_in_proj ? (size_t)nkv * d + (size_t)nv * dv : 0) + (size_t)extra_cols;
+        if (in_dtype == QT_F32)
+            launch_kernel(qk_row_rms_kernel<float>, dim3(n_tokens), dim3(256), 0, s, (const float*)qkv, n_splits, (size_t)split_stride, cols, nq * d,
+                          kv_in_proj ? nkv * d : 0, eps, row_inv);
+        else if (in_dtype == QT_BF16)
+            launch_kernel(qk_row_rms_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, s, (const __nv_bfloat16*)qkv, n_splits, (size_t)split_stride, cols,
+                          nq * d, kv_in_proj ? nkv * d : 0, eps, row_inv);
+        else QT_FAIL(QT_ERR_ARG, "qk_norm_rope_write: unsupported element type %d", in_dtype);
+        QT_CHECK_LAUNCH("qk_row_rms");
+    }
+    const bool vec = (!own_values || (nv * dv) % 8 == 0) && extra_cols % 8 == 0 && d % 8 == 0 && split_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
                      (!write_kv || (((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0)));
     // the register form: all dimensions rotate, half a head is one or two rounds of 32 or 64 elements, enough tokens
     // to fill the machine with a few heads per warp
@@ -651,7 +696,7 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
     const bool pair_aligned = split_stride % 2 == 0 && ((uintptr_t)qkv % 8 == 0) && ((uintptr_t)q_out % 8 == 0) && ((uintptr_t)cos_sin % 8 == 0) &&
                               (!q_weight || (uintptr_t)q_weight % 8 == 0) && (!k_weight || (uintptr_t)k_weight % 8 == 0) &&
                               (!write_kv || (((uintptr_t)k_cache % 8 == 0) && ((uintptr_t)v_cache % 8 == 0)));
-    if (pe && !own_values && pair_aligned && n_tokens >= 256 && nq + 2 * nkv <= 65535 * 16 && (in_dtype == QT_F32 || in_dtype == QT_BF16) && out_dtype == QT_BF16) {
+    if (pe && !own_values && !unit_norm && !whole_norm && !extra_cols && pair_aligned && n_tokens >= 256 && nq + 2 * nkv <= 65535 * 16 && (in_dtype == QT_F32 || in_dtype == QT_BF16) && out_dtype == QT_BF16) {
         const int heads_total = nq + (kv_in_proj ? 2 * nkv : 0);
         const dim3 pgrid((unsigned)n_tokens, (unsigned)((heads_total + warps * HEADS_PER_WARP - 1) / (warps * HEADS_PER_WARP)));
 #define QT_LAUNCH_PAIRS(TI, E, IT) launch_kernel(qk_norm_rope_pairs_kernel<TI, __nv_bfloat16, E, IT>, pgrid, dim3(warps * 32), 0, s, p)

@@ -36,6 +36,7 @@ struct ExpertParams {
     int gated; float limit;     // up holds [E, 2 ff, width]: ff gate rows, then ff up rows; mid = gated_value(g, u, act, limit)
     const float* base; int base_splits; size_t base_stride;   // [splits, T, width] float added to out, times row_scale[t]; or null
     const float* row_scale;     // [T] or null (1)
+    const float* in_weights;    // [T, top] or null: a pair's expert reads its token's row times this (a weight on the input, not the output)
 };
 
 __device__ __forceinline__ int expert_of(const ExpertParams& p, int t, int k) {
@@ -98,7 +99,8 @@ __global__ void __launch_bounds__(EV_WARPS * 32) expert_up_kernel(const ExpertPa
     const int pair = blockIdx.x, t = pair / p.top, k = pair % p.top;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const T* x = (const T*)p.x + (size_t)t * p.width;
-    for (int i = threadIdx.x; i < p.width; i += blockDim.x) xs[i] = to_float(x[i]);
+    const float in_weight = p.in_weights ? p.in_weights[pair] : 1.f;
+    for (int i = threadIdx.x; i < p.width; i += blockDim.x) xs[i] = to_float(x[i]) * in_weight;
     __syncthreads();
     const int e = expert_of(p, t, k);
     const T* w = (const T*)p.up + (size_t)e * (p.gated ? 2 : 1) * p.ff * p.width;
@@ -165,14 +167,14 @@ static int check_experts(const char* name, int n_tokens, int vocab, int top, int
 extern "C" int qt_experts_by_pair(const void* x, const int* token_ids, const int* table, const void* up, const void* down, void* mid,
                                   float* out, int dtype, int n_tokens, int vocab, int top, int experts, int width, int ff, int act,
                                   float pair_weight, const float* pair_weights, int gated, float limit, const float* base,
-                                  int base_splits, long long base_stride, const float* row_scale, void* stream) {
+                                  int base_splits, long long base_stride, const float* row_scale, const float* in_weights, void* stream) {
     QT_REQUIRE(gated || act < QT_ACT_COUNT, "experts_by_pair: activation %d needs gated experts", act);
     int rc = check_experts("experts_by_pair", n_tokens, vocab, top, experts, width, ff, act);
     if (rc) return rc;
     if (n_tokens == 0) return QT_OK;
     QT_REQUIRE((size_t)width * 4 <= 200 * 1024 && (size_t)top * ff * 4 <= 200 * 1024, "experts_by_pair: a row of %d or %d x %d floats does not fit shared memory", width, top, ff);
     ExpertParams p{x, token_ids, table, up, down, mid, out, n_tokens, vocab, top, experts, width, ff, act, pair_weight,
-                   pair_weights, gated, limit, base, base_splits, (size_t)base_stride, row_scale};
+                   pair_weights, gated, limit, base, base_splits, (size_t)base_stride, row_scale, in_weights};
     cudaStream_t s = (cudaStream_t)stream;
     const int per_block = EV_WARPS * EV_FEATS;
     return QT_DISPATCH_DTYPE(dtype, "experts_by_pair", {
@@ -202,7 +204,7 @@ extern "C" int qt_experts_by_pair(const void* x, const int* token_ids, const int
 // Routing for the tiled products (experts_tc.cu).  One block: count the pairs of every expert, give every expert a
 // run of rows padded to whole tiles of `tile_rows`, and give every pair a row in its expert's run.
 //   pair_row[pair]     the pair's row in the ordered buffers
-//   row_token[row]     the token whose (normed) input the row holds, -1 for padding
+//   row_token[row]     the pair whose token's (normed) input the row holds (the token is pair / top), -1 for padding
 //   tile_expert[tile]  the expert of the tile's rows, -1 for tiles beyond the last run
 // Which row of its run a pair gets depends on the order the threads arrive in; a row's results do not depend on where
 // it lies, so the output does not either.
@@ -238,17 +240,27 @@ __global__ void __launch_bounds__(1024) expert_route_kernel(const ExpertParams p
         const int e = expert_of(p, pair / p.top, pair % p.top);
         const int row = starts[e] + atomicAdd(&cursor[e], 1);
         pair_row[pair] = row;
-        row_token[row] = pair / p.top;
+        row_token[row] = pair;
     }
 }
 
-// ordered[row, :] = x[row_token[row], :] (zeros for padding rows).  One block per row, 16 bytes per thread and turn.
-__global__ void expert_gather_kernel(const uint4* __restrict__ x, const int* __restrict__ row_token, uint4* __restrict__ ordered, int chunks) {
+// ordered[row, :] = x[row_token[row] / top, :] (zeros for padding rows), times the pair's input weight where there is one
+// (the product in float, rounded once).  One block per row, 16 bytes per thread and turn.
+__global__ void expert_gather_kernel(const uint4* __restrict__ x, const int* __restrict__ row_token, uint4* __restrict__ ordered, int chunks, int top,
+                                     const float* __restrict__ in_weights) {
     pdl_launch_dependents();
     pdl_wait();
-    const int row = blockIdx.x, token = row_token[row];
-    for (int c = threadIdx.x; c < chunks; c += blockDim.x)
-        ordered[(size_t)row * chunks + c] = token >= 0 ? x[(size_t)token * chunks + c] : make_uint4(0u, 0u, 0u, 0u);
+    const int row = blockIdx.x, pair = row_token[row], token = pair >= 0 ? pair / top : -1;
+    const float w = (in_weights && pair >= 0) ? in_weights[pair] : 1.f;
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        uint4 v = token >= 0 ? x[(size_t)token * chunks + c] : make_uint4(0u, 0u, 0u, 0u);
+        if (in_weights) {
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(__low2float(h[j]) * w, __high2float(h[j]) * w);
+        }
+        ordered[(size_t)row * chunks + c] = v;
+    }
 }
 
 // out[t, :] = pair_weight * sum_k y[pair_row[t * top + k], :], in float, in the order of k.
@@ -272,11 +284,11 @@ __global__ void expert_combine_kernel(const T* __restrict__ y, const int* __rest
 
 // A learned router's choice.  logits [splits, T, cols] float (column e < experts: expert e; column `experts`, if
 // shared_gate, the logit of a shared expert's gate).  Scores are sigmoid(logit); the `top` largest are chosen (of equal
-// scores the lower expert first), their weights are the scores over their sum (+ 1e-20) times `scale`.
+// scores the lower expert first), their weights are the scores over their sum (+ 1e-20) times `scale`, or, without `normalize`, the scores themselves times `scale`.
 // One warp per token; chosen [T, top], weights [T, top], gate [T] = sigmoid of the extra column.
 __global__ void __launch_bounds__(128) route_top_kernel(const float* __restrict__ logits, int n_splits, size_t split_stride, int cols,
                                                         int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ gate,
-                                                        int n_tokens, int experts, int top, float scale) {
+                                                        int n_tokens, int experts, int top, float scale, int normalize) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float route_scores[];                      // [warps][experts]
@@ -303,25 +315,26 @@ __global__ void __launch_bounds__(128) route_top_kernel(const float* __restrict_
         __syncwarp();
     }
     if (lane < top) {
-        for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] = weights[(size_t)t * top + k] / (sum + 1e-20f) * scale;
+        for (int k = lane; k < top; k += 32)
+            weights[(size_t)t * top + k] = normalize ? weights[(size_t)t * top + k] / (sum + 1e-20f) * scale : weights[(size_t)t * top + k] * scale;
     }
 }
 
 extern "C" int qt_route_top(const float* logits, int n_splits, long long split_stride, int cols, int* chosen, float* weights, float* gate,
-                            int n_tokens, int experts, int top, float scale, void* stream) {
+                            int n_tokens, int experts, int top, float scale, int normalize, void* stream) {
     QT_REQUIRE(n_tokens >= 0 && experts > 0 && top > 0 && top <= experts && cols >= experts + (gate ? 1 : 0) && n_splits >= 1,
                "route_top: bad sizes T=%d E=%d top=%d cols=%d", n_tokens, experts, top, cols);
     QT_REQUIRE((size_t)4 * experts * sizeof(float) <= 48 * 1024, "route_top: %d experts are too many for a warp's scores in shared memory", experts);
     if (n_tokens == 0) return QT_OK;
     launch_kernel(route_top_kernel, dim3((n_tokens + 3) / 4), dim3(128), (size_t)4 * experts * sizeof(float), (cudaStream_t)stream, logits, n_splits,
-                  (size_t)split_stride, cols, chosen, weights, gate, n_tokens, experts, top, scale);
+                  (size_t)split_stride, cols, chosen, weights, gate, n_tokens, experts, top, scale, normalize);
     QT_CHECK_LAUNCH("route_top");
     return QT_OK;
 }
 
 extern "C" int qt_experts_route(const void* x, const int* token_ids, const int* table, void* ordered, int* pair_row, int* row_token,
                                 int* tile_expert, int n_tokens, int vocab, int top, int experts, int width, int tile_rows, int max_tiles,
-                                void* stream) {
+                                const float* in_weights, void* stream) {
     int rc = check_experts("experts_route", n_tokens, vocab, top, experts, width, 1, 0);
     if (rc) return rc;
     if (n_tokens == 0) return QT_OK;
@@ -329,11 +342,11 @@ extern "C" int qt_experts_route(const void* x, const int* token_ids, const int* 
     QT_REQUIRE(tile_rows > 0 && (long long)max_tiles * tile_rows >= (long long)n_tokens * top, "experts_route: %d tiles of %d rows do not hold the pairs", max_tiles, tile_rows);
     QT_REQUIRE((3 * (size_t)experts + 1) * sizeof(int) <= 48 * 1024, "experts_route: %d experts are too many for one block's counters", experts);
     ExpertParams p{x, token_ids, table, nullptr, nullptr, nullptr, nullptr, n_tokens, vocab, top, experts, width, 1, 0, 0.f,
-                   nullptr, 0, 0.f, nullptr, 1, 0, nullptr};
+                   nullptr, 0, 0.f, nullptr, 1, 0, nullptr, nullptr};
     cudaStream_t s = (cudaStream_t)stream;
     launch_kernel(expert_route_kernel, dim3(1), dim3(1024), (3 * (size_t)experts + 1) * sizeof(int), s, p, pair_row, row_token, tile_expert, tile_rows, max_tiles);
     QT_CHECK_LAUNCH("expert_route");
-    launch_kernel(expert_gather_kernel, dim3(max_tiles * tile_rows), dim3(128), 0, s, (const uint4*)x, (const int*)row_token, (uint4*)ordered, width / 8);
+    launch_kernel(expert_gather_kernel, dim3(max_tiles * tile_rows), dim3(128), 0, s, (const uint4*)x, (const int*)row_token, (uint4*)ordered, width / 8, top, in_weights);
     QT_CHECK_LAUNCH("expert_gather");
     return QT_OK;
 }

@@ -1,10 +1,11 @@
-// Layer norm without bias around the float residual stream, and an activation on a product's sums.
+// Layer norm (with or without bias) around the float residual stream, and an activation on a product's sums.
 //
 // add_layernorm_kernel: one block per output row r, src = rows ? rows[r] : r.
 //   d = sum_s delta[s][src]                                   (float; split-K partial sums added in their order)
-//   if (post_weight) d = (d - mean(d)) / sqrt(var(d) + eps) * post_weight     (a norm on the sublayer's output)
+//   if (post_weight) d = (d - mean(d)) / sqrt(var(d) + eps) * post_weight (+ post_bias)   (a norm on the sublayer's output)
 //   x = residual[src] + d;  if (!rows) residual[src] = x      (the stream is updated in place)
-//   out[r] = (x - mean(x)) / sqrt(var(x) + eps) * weight      (rounded once to the output type)
+//   out[r] = (x - mean(x)) / sqrt(var(x) + eps) * weight (+ bias)     (rounded once to the output type)
+//   without `weight`: out[r] = x                              (a sublayer that reads the stream itself)
 // The variance is the mean of the squared deviations from the mean, taken in a second pass over the row, which the
 // block keeps in shared memory.  A layer that norms what a sublayer returns before adding it, and norms the stream
 // again for the next sublayer, is one launch per sublayer.
@@ -18,7 +19,8 @@ using namespace qt;
 
 template <typename TD, typename TO>
 __global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_splits, size_t split_stride,
-                                     const float* __restrict__ post_weight, const float* __restrict__ weight, float eps,
+                                     const float* __restrict__ post_weight, const float* __restrict__ post_bias,
+                                     const float* __restrict__ weight, const float* __restrict__ bias, float eps,
                                      TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
     pdl_launch_dependents();
     pdl_wait();
@@ -43,7 +45,7 @@ __global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __r
                 sq += c * c;
             }
             const float inv = rsqrtf(block_sum(sq, scratch) * inv_n + eps);
-            for (int i = threadIdx.x; i < hidden; i += blockDim.x) row[i] = (row[i] - mean) * inv * post_weight[i];
+            for (int i = threadIdx.x; i < hidden; i += blockDim.x) row[i] = (row[i] - mean) * inv * post_weight[i] + (post_bias ? post_bias[i] : 0.f);
         }
     }
     float sum = 0.f;
@@ -53,6 +55,11 @@ __global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __r
         if (!rows) res[i] = x;
         sum += x;
     }
+    TO* o = out + (size_t)r * hidden;
+    if (!weight) {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<TO>(row[i]);      // each thread reads what it wrote
+        return;
+    }
     const float mean = block_sum(sum, scratch) * inv_n;
     float sq = 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
@@ -60,8 +67,7 @@ __global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __r
         sq += c * c;
     }
     const float inv = rsqrtf(block_sum(sq, scratch) * inv_n + eps);
-    TO* o = out + (size_t)r * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<TO>((row[i] - mean) * inv * weight[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<TO>((row[i] - mean) * inv * weight[i] + (bias ? bias[i] : 0.f));
 }
 
 // The same for rows of up to 4,096 elements whose length and strides are multiples of four: a thread holds four elements
@@ -86,7 +92,8 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
 
 template <typename TD, typename TO>
 __global__ void add_layernorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_splits, size_t split_stride,
-                                         const float* __restrict__ post_weight, const float* __restrict__ weight, float eps,
+                                         const float* __restrict__ post_weight, const float* __restrict__ post_bias,
+                                         const float* __restrict__ weight, const float* __restrict__ bias, float eps,
                                          TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
     pdl_launch_dependents();
     pdl_wait();
@@ -98,11 +105,13 @@ __global__ void add_layernorm_vec_kernel(float* __restrict__ residual, const TD*
     const int i = threadIdx.x;
     const bool has = i < (hidden >> 2);              // a thread holds one quad of the row in registers (blockDim.x >= hidden / 4)
     // everything the thread reads is asked for at once: the sums, the stream and both weights
-    float4 x = make_float4(0.f, 0.f, 0.f, 0.f), d = x, w = x, pw = x;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f), d = x, w = x, pw = x, b = x, pb = x;
     if (has) {
         x = load4(res + 4 * i);
-        w = load4(weight + 4 * i);
+        if (weight) w = load4(weight + 4 * i);
+        if (bias) b = load4(bias + 4 * i);
         if (post_weight) pw = load4(post_weight + 4 * i);
+        if (post_bias) pb = load4(post_bias + 4 * i);
         if (delta) {
             const TD* at = delta + (size_t)src * hidden + 4 * i;
             d = load4(at);
@@ -114,24 +123,29 @@ __global__ void add_layernorm_vec_kernel(float* __restrict__ residual, const TD*
     }
     if (delta && post_weight) {
         const float mean = block_sum((d.x + d.y) + (d.z + d.w), scratch) * inv_n;
-        const float a = d.x - mean, b = d.y - mean, c = d.z - mean, e = d.w - mean;
-        const float inv = rsqrtf(block_sum(has ? (a * a + b * b) + (c * c + e * e) : 0.f, scratch) * inv_n + eps);
-        d = make_float4(a * inv * pw.x, b * inv * pw.y, c * inv * pw.z, e * inv * pw.w);
+        const float a = d.x - mean, g = d.y - mean, c = d.z - mean, e = d.w - mean;
+        const float inv = rsqrtf(block_sum(has ? (a * a + g * g) + (c * c + e * e) : 0.f, scratch) * inv_n + eps);
+        d = make_float4(a * inv * pw.x + pb.x, g * inv * pw.y + pb.y, c * inv * pw.z + pb.z, e * inv * pw.w + pb.w);
     }
     if (delta) { x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w; }
     if (!rows && has) store4(res + 4 * i, x);
+    if (!weight) {
+        if (has) store4(out + (size_t)r * hidden + 4 * i, x);
+        return;
+    }
     const float mean = block_sum((x.x + x.y) + (x.z + x.w), scratch) * inv_n;
-    const float a = x.x - mean, b = x.y - mean, c = x.z - mean, e = x.w - mean;
-    const float inv = rsqrtf(block_sum(has ? (a * a + b * b) + (c * c + e * e) : 0.f, scratch) * inv_n + eps);
-    if (has) store4(out + (size_t)r * hidden + 4 * i, make_float4(a * inv * w.x, b * inv * w.y, c * inv * w.z, e * inv * w.w));
+    const float a = x.x - mean, g = x.y - mean, c = x.z - mean, e = x.w - mean;
+    const float inv = rsqrtf(block_sum(has ? (a * a + g * g) + (c * c + e * e) : 0.f, scratch) * inv_n + eps);
+    if (has) store4(out + (size_t)r * hidden + 4 * i, make_float4(a * inv * w.x + b.x, g * inv * w.y + b.y, c * inv * w.z + b.z, e * inv * w.w + b.w));
 }
 
 extern "C" int qt_add_layernorm(float* residual, const void* delta, int delta_dtype, int n_splits, long long split_stride,
-                                const float* post_weight, const float* weight, float eps, void* out, int out_dtype, const int* rows,
-                                int n_rows, int hidden, void* stream) {
+                                const float* post_weight, const float* post_bias, const float* weight, const float* bias, float eps,
+                                void* out, int out_dtype, const int* rows, int n_rows, int hidden, void* stream) {
     QT_REQUIRE(n_rows >= 0 && hidden > 0 && n_splits >= 1, "add_layernorm: bad sizes rows=%d H=%d splits=%d", n_rows, hidden, n_splits);
     QT_REQUIRE(eps > 0.f, "add_layernorm: eps must be positive");
     QT_REQUIRE(delta || !post_weight, "add_layernorm: a norm on an addition that is not there");
+    QT_REQUIRE((post_weight || !post_bias) && (weight || !bias), "add_layernorm: a bias without its weight");
     if (n_rows == 0) return QT_OK;
     const size_t smem = (size_t)hidden * sizeof(float);
     QT_REQUIRE(smem <= 200 * 1024, "add_layernorm: a row of %d elements does not fit shared memory", hidden);
@@ -141,7 +155,7 @@ extern "C" int qt_add_layernorm(float* residual, const void* delta, int delta_dt
     // rows of at most 1,024 whole quads whose every pointer and stride keeps 16-byte alignment go four elements a thread
     const auto misaligned = [](const void* ptr) { return ((uintptr_t)ptr & 15) != 0; };
     const bool vec = hidden % 4 == 0 && hidden <= 4 * threads && split_stride % 4 == 0 && !misaligned(residual) && !misaligned(delta) && !misaligned(post_weight) &&
-                     !misaligned(weight) && !misaligned(out);
+                     !misaligned(weight) && !misaligned(out) && !misaligned(bias) && !misaligned(post_bias);
 #define QT_LAUNCH_LN(TD, TO)                                                                                                        \
     do {                                                                                                                            \
         if (smem > 48 * 1024) {                                                                                                     \
@@ -150,10 +164,10 @@ extern "C" int qt_add_layernorm(float* residual, const void* delta, int delta_dt
         }                                                                                                                           \
         if (vec)                                                                                                                    \
             launch_kernel(add_layernorm_vec_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, s, residual, (const TD*)delta, n_splits, \
-                          (size_t)split_stride, post_weight, weight, eps, (TO*)out, rows, hidden);                                  \
+                          (size_t)split_stride, post_weight, post_bias, weight, bias, eps, (TO*)out, rows, hidden);                                  \
         else                                                                                                                        \
             launch_kernel(add_layernorm_kernel<TD, TO>, dim3(n_rows), dim3(threads), smem, s, residual, (const TD*)delta, n_splits, \
-                          (size_t)split_stride, post_weight, weight, eps, (TO*)out, rows, hidden);                                  \
+                          (size_t)split_stride, post_weight, post_bias, weight, bias, eps, (TO*)out, rows, hidden);                                  \
     } while (0)
     if (delta_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_LN(float, float);
     else if (delta_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_LN(float, __nv_bfloat16);
@@ -216,6 +230,37 @@ extern "C" int qt_activation(const void* in, int in_dtype, int n_splits, long lo
     else QT_FAIL(QT_ERR_ARG, "activation: unknown element types %d/%d", in_dtype, out_dtype);
 #undef QT_LAUNCH_ACT
     QT_CHECK_LAUNCH("activation");
+    return QT_OK;
+}
+
+// ----------------------------------------------------------------------------- a weighted sum of two products' sums
+// out = wa * sum_s a[s] + wb * sum_s b[s], in float: two sublayers that run side by side on the same input and are
+// mixed with two constants before anything else happens to them.
+template <typename TA, typename TB>
+__global__ void weighted_sum_kernel(const TA* __restrict__ a, int a_splits, size_t a_stride, float wa, const TB* __restrict__ b, int b_splits,
+                                    size_t b_stride, float wb, float* __restrict__ out, long long total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+        out[i] = wa * load_sum(a, (size_t)i, a_splits, a_stride) + wb * load_sum(b, (size_t)i, b_splits, b_stride);
+}
+
+extern "C" int qt_weighted_sum(const void* a, int a_dtype, int a_splits, long long a_stride, float wa, const void* b, int b_dtype, int b_splits,
+                               long long b_stride, float wb, float* out, long long total, void* stream) {
+    QT_REQUIRE(total >= 0 && a_splits >= 1 && b_splits >= 1, "weighted_sum: bad sizes");
+    if (total == 0) return QT_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    long long blocks = (total + 255) / 256;
+    if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
+#define QT_LAUNCH_WS(TA, TB) launch_kernel(weighted_sum_kernel<TA, TB>, dim3((unsigned)blocks), dim3(256), 0, s, (const TA*)a, a_splits, (size_t)a_stride, wa, \
+                                           (const TB*)b, b_splits, (size_t)b_stride, wb, out, total)
+    if (a_dtype == QT_F32 && b_dtype == QT_F32) QT_LAUNCH_WS(float, float);
+    else if (a_dtype == QT_F32 && b_dtype == QT_BF16) QT_LAUNCH_WS(float, __nv_bfloat16);
+    else if (a_dtype == QT_BF16 && b_dtype == QT_F32) QT_LAUNCH_WS(__nv_bfloat16, float);
+    else if (a_dtype == QT_BF16 && b_dtype == QT_BF16) QT_LAUNCH_WS(__nv_bfloat16, __nv_bfloat16);
+    else QT_FAIL(QT_ERR_ARG, "weighted_sum: unknown element types %d/%d", a_dtype, b_dtype);
+#undef QT_LAUNCH_WS
+    QT_CHECK_LAUNCH("weighted_sum");
     return QT_OK;
 }
 

@@ -8,7 +8,8 @@
 //                        into the paged cache at the token's position).  Values are the keys, so nothing else is stored.
 // conv_keep_kernel       kept[slot] <- the raw inputs of the sequence's last n - 1 positions after this step.
 // gate_mul_kernel        x[t][c] *= sigmoid(sum_s gate[s][t][offset + c]): a gate computed from the mixer's input by one
-//                        more block of rows of the first projection.
+//                        more block of rows of the first projection.  With `group` > 1 every `group` consecutive
+//                        columns share one gate column (one number per head).
 #include "common.cuh"
 
 #include <math.h>
@@ -116,20 +117,21 @@ extern "C" int qt_conv_qk_write(const float* proj, int n_splits, long long split
 // ----------------------------------------------------------------------------- sigmoid gate on the heads' outputs
 template <typename T>
 __global__ void gate_mul_kernel(T* __restrict__ x, const float* __restrict__ gate, int n_splits, size_t split_stride, int gate_cols,
-                                int gate_offset, long long total, int cols) {
+                                int gate_offset, long long total, int cols, int group) {
     pdl_launch_dependents();
     pdl_wait();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const long long t = i / cols;
         const int c = (int)(i % cols);
-        const float g = sum_splits(gate, (size_t)t * gate_cols + gate_offset + c, n_splits, split_stride);
+        const float g = sum_splits(gate, (size_t)t * gate_cols + gate_offset + c / group, n_splits, split_stride);
         x[i] = from_float<T>(to_float(x[i]) / (1.f + expf(-g)));
     }
 }
 
 extern "C" int qt_gate_mul(void* x, int dtype, const float* gate, int n_splits, long long split_stride, int gate_cols, int gate_offset,
-                           int n_rows, int cols, void* stream) {
-    QT_REQUIRE(n_rows >= 0 && cols > 0 && gate_offset >= 0 && gate_offset + cols <= gate_cols && n_splits >= 1,
+                           int n_rows, int cols, int group, void* stream) {
+    if (group <= 0) group = 1;
+    QT_REQUIRE(n_rows >= 0 && cols > 0 && gate_offset >= 0 && gate_offset + (cols + group - 1) / group <= gate_cols && n_splits >= 1,
                "gate_mul: %d columns at %d of %d", cols, gate_offset, gate_cols);
     if (n_rows == 0) return QT_OK;
     cudaStream_t s = (cudaStream_t)stream;
@@ -138,7 +140,7 @@ extern "C" int qt_gate_mul(void* x, int dtype, const float* gate, int n_splits, 
     if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
     return QT_DISPATCH_DTYPE(dtype, "gate_mul", {
         launch_kernel(gate_mul_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, s, (T*)x, gate, n_splits, (size_t)split_stride, gate_cols,
-                      gate_offset, total, cols);
+                      gate_offset, total, cols, group);
         QT_CHECK_LAUNCH("gate_mul");
         return QT_OK;
     });

@@ -31,7 +31,7 @@ _SIGNATURES = {
                                _c_int, _c_int, _c_ptr],
         "qt_qk_norm_rope_write": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                                   _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_ptr],
         "qt_swiglu": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr],
         "qt_add_dyt": [_c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_ptr, _c_int,
                        _c_int, _c_ptr],
@@ -46,22 +46,29 @@ _SIGNATURES = {
         "qt_delta_scan_chunked": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     },
+    "linear_attention": {
+        "qt_linear_attention_scan": [_c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int,
+                                     _c_int, _c_int, _c_int, _c_int, _c_ptr],
+        "qt_linear_attention_gate_norm": [_c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr, _c_float, _c_float, _c_ptr, _c_int, _c_int,
+                                          _c_int, _c_ptr],
+    },
     "attention": {
         "qt_attention_prefill": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int,
                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_int, _c_int,
-                                 _c_int, _c_int, _c_int, _c_ptr],
+                                 _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
         "qt_attention_decode": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int,
                                 _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int,
-                                _c_int, _c_int, _c_int, _c_ptr],
+                                _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     },
     "layernorm": {
-        "qt_add_layernorm": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_ptr],
+        "qt_add_layernorm": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_ptr],
+        "qt_weighted_sum": [_c_ptr, _c_int, _c_int, _c_ll, _c_float, _c_ptr, _c_int, _c_int, _c_ll, _c_float, _c_ptr, _c_ll, _c_ptr],
         "qt_activation": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     },
     "short_conv": {
         "qt_conv_qk_write": [_c_ptr, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,
                              _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
-        "qt_gate_mul": [_c_ptr, _c_int, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+        "qt_gate_mul": [_c_ptr, _c_int, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     },
     "latent": {
         "qt_latent_prepare": [_c_ptr, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr,
@@ -79,10 +86,10 @@ _SIGNATURES = {
     },
     "experts": {
         "qt_experts_by_pair": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
-                               _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_int, _c_float, _c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr],
-        "qt_route_top": [_c_ptr, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_float, _c_ptr],
+                               _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_int, _c_float, _c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ptr],
+        "qt_route_top": [_c_ptr, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr],
         "qt_experts_route": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                             _c_int, _c_ptr],
+                             _c_int, _c_ptr, _c_ptr],
         "qt_experts_combine": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr],
     },
     "experts_tc": {
@@ -93,9 +100,9 @@ _SIGNATURES = {
                                     _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr],
         "qt_attention_decode_ws": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                                    _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
-                                   _c_int, _c_int, _c_ptr],
+                                   _c_int, _c_int, _c_ptr, _c_ptr],
         "qt_attention_prefill_mma": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
-                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     },
     "attention_tc": {
         "qt_attention_prefill_tc": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
@@ -328,8 +335,13 @@ def qk_norm_rope_write(qkv: GemmOut, q_out: torch.Tensor, k_cache: torch.Tensor 
                        q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
                        cos_sin: torch.Tensor | None, num_heads: int, num_kv_heads: int, head_dim: int,
                        page_tokens: int, ring_tokens: int, write_kv: bool = True, kv_in_proj: bool = True,
-                       interleaved: bool = False, v_heads: int | None = None, v_head_dim: int | None = None) -> None:
+                       interleaved: bool = False, v_heads: int | None = None, v_head_dim: int | None = None, unit_norm: bool = False,
+                       row_inv: torch.Tensor | None = None, extra_cols: int = 0) -> None:
     """Per-head q/k RMSNorm, rotation and the cache write, from the fused projection output.
+
+    ``unit_norm``: q and k heads are divided by their root mean square without a weight (no q_weight / k_weight).
+    ``row_inv`` (float scratch [T, 2]): q and k are normed over all their heads at once, with weights [nq d] and [nkv d].
+    ``extra_cols``: further columns of the projection behind q, k and v, which are left alone.
 
     qkv [*, T, (nq + 2 nkv) d]; q_out [T, nq, d]; caches [pages, nkv, page_tokens, d]; cos_sin float [P, rd]
     (cos | sin of the rd/2 pair angles); pairs are (i, i + rd/2), or (2i, 2i + 1) with ``interleaved``.
@@ -338,15 +350,18 @@ def qk_norm_rope_write(qkv: GemmOut, q_out: torch.Tensor, k_cache: torch.Tensor 
     """
     tokens = qkv.rows
     nv, dv = int(v_heads or num_kv_heads), int(v_head_dim or head_dim)
-    width = num_heads * head_dim + ((num_kv_heads * head_dim + nv * dv) if kv_in_proj else 0)
+    width = num_heads * head_dim + ((num_kv_heads * head_dim + nv * dv) if kv_in_proj else 0) + int(extra_cols)
+    whole = row_inv is not None
+    if whole:
+        _need(row_inv, "row_inv", torch.float32, (tokens, 2))
     if qkv.cols != width:
         raise KernelError(f"qk_norm_rope_write: projection width {qkv.cols} != nq d + nkv d + nv dv = {width}")
     _need(q_out, "q_out", shape=(tokens, num_heads, head_dim))
     _need(token_seq, "token_seq", torch.int32, (tokens,))
     _need(token_pos, "token_pos", torch.int32, (tokens,))
-    for name, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+    for name, w, heads in (("q_weight", q_weight, num_heads), ("k_weight", k_weight, num_kv_heads)):
         if w is not None:
-            _need(w, name, torch.float32, (head_dim,))
+            _need(w, name, torch.float32, (heads * head_dim if whole else head_dim,))
     rotary_dim, max_pos = 0, 0
     if cos_sin is not None:
         _need(cos_sin, "cos_sin", torch.float32)
@@ -363,7 +378,8 @@ def qk_norm_rope_write(qkv: GemmOut, q_out: torch.Tensor, k_cache: torch.Tensor 
           qkv.split_stride, _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _code(q_out, "q_out"), _ptr(token_seq),
           _ptr(token_pos), _ptr(block_table), max_blocks, _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos_sin),
           rotary_dim, max_pos, tokens, num_heads, num_kv_heads, head_dim, page_tokens, ring_tokens,
-          1 if write_kv else 0, 1 if kv_in_proj else 0, 1 if interleaved else 0, nv, dv, _stream())
+          1 if write_kv else 0, 1 if kv_in_proj else 0, 1 if interleaved else 0, nv, dv, 1 if unit_norm else 0, 1 if whole else 0,
+          _ptr(row_inv), int(extra_cols), _stream())
 
 
 def add_dyt(residual: torch.Tensor, deltas, weight: torch.Tensor, bias: torch.Tensor, alpha: float, out: torch.Tensor,
@@ -405,18 +421,20 @@ def map_difference(ctx: torch.Tensor, out: torch.Tensor, lam: float, eps: float,
           float(post), _stream())
 
 
-def add_layernorm(residual: torch.Tensor, delta: GemmOut | None, post_weight: torch.Tensor | None, weight: torch.Tensor, eps: float,
-                  out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
-    """Layer norm without bias around the float stream: d = delta, normed with ``post_weight`` first where that is given;
-    stream += d; out = (stream - mean) / sqrt(var + eps) * weight, the variance being the mean squared deviation.
+def add_layernorm(residual: torch.Tensor, delta: GemmOut | None, post_weight: torch.Tensor | None, weight: torch.Tensor | None, eps: float,
+                  out: torch.Tensor, rows: torch.Tensor | None = None, post_bias: torch.Tensor | None = None,
+                  bias: torch.Tensor | None = None) -> None:
+    """Layer norm around the float stream: d = delta, normed with ``post_weight`` (and ``post_bias``) first where that is given;
+    stream += d; out = (stream - mean) / sqrt(var + eps) * weight (+ ``bias``), the variance being the mean squared deviation.
+    Without ``weight`` the new stream itself is written to ``out`` (in its element type).
 
     Without ``rows`` every row of ``residual`` [T, H] is updated in place and normed into ``out`` [T, H]; with ``rows``
     (int32 [K]) only those rows are normed into ``out`` [K, H] and the stream is left as it is."""
     hidden = residual.shape[1]
     _need(residual, "residual", torch.float32)
-    _need(weight, "weight", torch.float32, (hidden,))
-    if post_weight is not None:
-        _need(post_weight, "post_weight", torch.float32, (hidden,))
+    for name, vector in (("weight", weight), ("post_weight", post_weight), ("bias", bias), ("post_bias", post_bias)):
+        if vector is not None:
+            _need(vector, name, torch.float32, (hidden,))
     n_rows = residual.shape[0] if rows is None else rows.shape[0]
     _need(out, "out", shape=(n_rows, hidden))
     if rows is not None:
@@ -425,7 +443,20 @@ def add_layernorm(residual: torch.Tensor, delta: GemmOut | None, post_weight: to
         raise KernelError(f"add_layernorm: delta {tuple(delta.tensor.shape)} does not match the stream {tuple(residual.shape)}")
     _call("layernorm", "qt_add_layernorm", _ptr(residual), _ptr(delta.tensor) if delta else None,
           _code(delta.tensor, "delta") if delta else F32, delta.n_splits if delta else 1, delta.split_stride if delta else 0,
-          _ptr(post_weight), _ptr(weight), float(eps), _ptr(out), _code(out, "out"), _ptr(rows), n_rows, hidden, _stream())
+          _ptr(post_weight), _ptr(post_bias), _ptr(weight), _ptr(bias), float(eps), _ptr(out), _code(out, "out"), _ptr(rows), n_rows, hidden,
+          _stream())
+
+
+def weighted_sum(a: GemmOut, wa: float, b: GemmOut, wb: float, out: torch.Tensor) -> GemmOut:
+    """out [T, N] (float) = wa * a + wb * b, the two products' split sums added in their order."""
+    if (a.rows, a.cols) != (b.rows, b.cols):
+        raise KernelError(f"weighted_sum: {tuple(a.tensor.shape)} and {tuple(b.tensor.shape)}")
+    _need(a.tensor, "a")
+    _need(b.tensor, "b")
+    _need(out, "out", torch.float32, (a.rows, a.cols))
+    _call("layernorm", "qt_weighted_sum", _ptr(a.tensor), _code(a.tensor, "a"), a.n_splits, a.split_stride, float(wa), _ptr(b.tensor),
+          _code(b.tensor, "b"), b.n_splits, b.split_stride, float(wb), _ptr(out), a.rows * a.cols, _stream())
+    return GemmOut(out.view(1, a.rows, a.cols))
 
 
 def activation(x: GemmOut, out: torch.Tensor, name: str = "gelu") -> None:
@@ -464,14 +495,15 @@ def conv_qk_write(proj: GemmOut, taps: torch.Tensor, kept: torch.Tensor, ctx, q_
           1 if write_kv else 0, _stream(), launches=2 if n_taps > 1 else 1)
 
 
-def gate_mul(x: torch.Tensor, gate: GemmOut, offset: int) -> None:
-    """x [T, N] *= sigmoid(columns ``offset`` .. ``offset + N`` of ``gate``), in float, in place."""
+def gate_mul(x: torch.Tensor, gate: GemmOut, offset: int, group: int = 1) -> None:
+    """x [T, N] *= sigmoid(columns ``offset`` .. ``offset + N`` of ``gate``), in float, in place.  With ``group`` > 1 every
+    ``group`` consecutive columns of x share one gate column (one number per head): columns ``offset`` .. ``offset + N / group``."""
     _need(x, "x")
     _need(gate.tensor, "gate", torch.float32)
     if x.dim() != 2 or gate.rows != x.shape[0]:
         raise KernelError(f"gate_mul: x {tuple(x.shape)} and a gate of {gate.rows} rows")
     _call("short_conv", "qt_gate_mul", _ptr(x), _code(x, "x"), _ptr(gate.tensor), gate.n_splits, gate.split_stride, gate.cols, int(offset),
-          x.shape[0], x.shape[1], _stream())
+          x.shape[0], x.shape[1], int(group), _stream())
 
 
 def latent_prepare(proj: GemmOut, q_norm: torch.Tensor, kv_norm: torch.Tensor | None, eps: float, cos_sin: torch.Tensor | None,
@@ -648,6 +680,42 @@ def gated_head_norm(o: torch.Tensor, gate: torch.Tensor | None, weight: torch.Te
           vdim, _stream())
 
 
+LINEAR_ATTENTION_MAX_DIM = 256     # key channels per head that the decayed linear attention's kernel holds
+
+
+def linear_attention_scan(proj: GemmOut, at_q: int, at_k: int, at_v: int, decay: torch.Tensor, state: torch.Tensor, out: torch.Tensor,
+                          ctx, dim: int, act: bool = True) -> None:
+    """Linear attention with a constant decay per head over the step's packed sequences: per head S <- decay_h S + k_t v_t^T,
+    o_t = S^T q_t, float throughout.  q, k ([heads, dim]) and v ([heads, vdim]) are the columns of ``proj`` (float sums
+    [*, T, cols]) from ``at_q``, ``at_k``, ``at_v`` on, and pass SiLU first where ``act``.  ``state`` [slots, heads, vdim, dim]
+    (the state transposed) is read and written at the rows ``ctx.slots`` names; ``out`` [T, heads, vdim]."""
+    tokens, heads, vdim = out.shape
+    _need(proj.tensor, "proj", torch.float32)
+    _need(out, "out", torch.float32)
+    _need(decay, "decay", torch.float32, (heads,))
+    _need(state, "state", torch.float32)
+    if proj.rows != tokens or tuple(state.shape[1:]) != (heads, vdim, dim):
+        raise KernelError(f"linear_attention_scan: state {tuple(state.shape)} is not [slots, {heads}, {vdim}, {dim}], or {proj.rows} rows for {tokens} tokens")
+    _call("linear_attention", "qt_linear_attention_scan", _ptr(proj.tensor), proj.n_splits, proj.split_stride, proj.cols, int(at_q), int(at_k),
+          int(at_v), _ptr(decay), _ptr(state), _ptr(out), _ptr(ctx.seq_start), _ptr(ctx.slots), ctx.n_seqs, heads, int(dim), vdim,
+          1 if act else 0, _stream())
+
+
+def linear_attention_gate_norm(o: torch.Tensor, proj: GemmOut | None, at_gate: int, weight: torch.Tensor, eps: float, scale: float,
+                               out: torch.Tensor) -> None:
+    """out [T, N] = o / sqrt(mean(o^2) + eps) * weight * sigmoid(columns ``at_gate`` .. of ``proj``) * scale, the mean over the
+    token's whole row (all heads at once); o float, rounded once to ``out``'s type."""
+    tokens, width = o.shape
+    _need(o, "o", torch.float32)
+    _need(weight, "weight", torch.float32, (width,))
+    _need(out, "out", shape=(tokens, width))
+    if proj is not None:
+        _need(proj.tensor, "proj", torch.float32)
+    _call("linear_attention", "qt_linear_attention_gate_norm", _ptr(o), _ptr(proj.tensor) if proj is not None else None,
+          proj.n_splits if proj is not None else 1, proj.split_stride if proj is not None else 0, proj.cols if proj is not None else 0,
+          int(at_gate), _ptr(weight), float(eps), float(scale), _ptr(out), _code(out, "out"), tokens, width, _stream())
+
+
 SWIGLU_GROUP = 16      # rows of gate and of up that alternate in a weight laid out for the GEMM's gated epilogue
 # gate activations of a gated feed-forward, act(gate) * up: names a configuration may use -> the kernels' codes
 ACTIVATIONS = {"silu": 0, "swish": 0, "gelu_pytorch_tanh": 1, "gelu_tanh": 1, "gelu": 2, "relu": 3}
@@ -807,7 +875,8 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
                       block_table: torch.Tensor, seq_start: torch.Tensor, seq_past: torch.Tensor, max_q_len: int,
                       num_kv_heads: int, page_tokens: int, ring_tokens: int, window: int | None, scale: float,
                       impl: str | None = None, penalty: tuple[torch.Tensor, torch.Tensor] | None = None,
-                      chunk: int | None = None, keep_first: int = 0, sink: bool = False, v_dim: int | None = None) -> None:
+                      chunk: int | None = None, keep_first: int = 0, sink: bool = False, v_dim: int | None = None,
+                      sinks: torch.Tensor | None = None) -> None:
     """Causal attention of packed sequences over the cache (which already holds this step's keys).
     ``chunk``: a query at position i sees key j only if i // chunk == j // chunk as well.  A value cache with fewer
     heads than the key cache serves key head g with value head g % (value heads).
@@ -815,9 +884,12 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     ``penalty`` = (r1, r2), float [heads] each: the score of key j for the query at position i loses
     r1_h * ln(1 + r2_h * (i - j)); ``penalty`` = (slopes, None): it loses slope_h * (i - j).
     ``keep_first``: a windowed query also sees the keys at positions below it.  ``sink``: the softmax has one more term
-    of score 0 without a value.  ``v_dim``: the values are the first ``v_dim`` elements of the rows of ``v_cache`` (which
+    of score 0 without a value, or, with ``sinks`` (float [heads]), of the head's own score, taken as it is (not scaled).  ``v_dim``: the values are the first ``v_dim`` elements of the rows of ``v_cache`` (which
     may be the key cache itself)."""
     _, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty, v_dim)
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32, (num_heads,))
+        sink = True
     if impl in (None, "latent") and attention_latent_supported(q, k_cache, v_cache, num_kv_heads, page_tokens, ring_tokens, window, scale, penalty,
                                                                chunk, keep_first, sink, v_dim):
         n_seqs = seq_past.shape[0]
@@ -852,13 +924,13 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
               _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, int(max_q_len), num_heads,
               num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale),
               _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, int(chunk or 0), v_cache.shape[1],
-              int(keep_first), 1 if sink else 0, _stream())
+              int(keep_first), 1 if sink else 0, _ptr(sinks), _stream())
         return
     _call("attention", "qt_attention_prefill", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q, "q"),
           _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, int(max_q_len), num_heads,
           num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale), int(v_dim or v_cache.shape[-1]),
           _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, int(chunk or 0), v_cache.shape[1],
-          int(keep_first), 1 if sink else 0, v_cache.shape[-1], _stream())
+          int(keep_first), 1 if sink else 0, v_cache.shape[-1], _ptr(sinks), _stream())
 
 
 def _ws_merges_in_cluster(n_splits: int, warps: int, group: int, head_dim: int) -> bool:
@@ -878,7 +950,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      ring_tokens: int, window: int | None, scale: float, n_splits: int,
                      part_acc: torch.Tensor | None, part_ml: torch.Tensor | None, impl: str | None = None,
                      warps: int = 1, penalty: tuple[torch.Tensor, torch.Tensor] | None = None, chunk: int | None = None,
-                     keep_first: int = 0, sink: bool = False, v_dim: int | None = None) -> None:
+                     keep_first: int = 0, sink: bool = False, v_dim: int | None = None, sinks: torch.Tensor | None = None) -> None:
     """One query token per sequence; ``seq_len`` counts the keys it sees (its own included).
 
     With ``n_splits`` > 1 the keys of each sequence are cut into that many ranges whose partial
@@ -889,6 +961,9 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     """
     n_seqs, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty, v_dim)
     _need(seq_len, "seq_len", torch.int32, (n_seqs,))
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32, (num_heads,))
+        sink = True
     if impl in (None, "latent") and attention_latent_supported(q, k_cache, v_cache, num_kv_heads, page_tokens, ring_tokens, window, scale, penalty,
                                                                chunk, keep_first, sink, v_dim):
         if n_splits > 1:
@@ -925,20 +1000,22 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     if picked == "ws":
         _call("attention_mma", "qt_attention_decode_ws", *common, int(warps), _ptr(part_acc), _ptr(part_ml),
               _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, int(chunk or 0), v_cache.shape[1],
-              int(keep_first), 1 if sink else 0, _stream(), launches=launches)
+              int(keep_first), 1 if sink else 0, _ptr(sinks), _stream(), launches=launches)
     elif picked == "mma":
         _call("attention_mma", "qt_attention_decode_mma", *common, _ptr(part_acc), _ptr(part_ml), _stream(), launches=launches)
     else:
         _call("attention", "qt_attention_decode", *common[:4], _code(q, "q"), *common[4:], _ptr(part_acc), _ptr(part_ml),
               int(v_dim or v_cache.shape[-1]), _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None,
-              int(chunk or 0), v_cache.shape[1], int(keep_first), 1 if sink else 0, v_cache.shape[-1], _stream(), launches=launches)
+              int(chunk or 0), v_cache.shape[1], int(keep_first), 1 if sink else 0, v_cache.shape[-1], _ptr(sinks), _stream(), launches=launches)
 
 
 # ----------------------------------------------------------------------------- experts chosen by a table
-def route_top(logits: GemmOut, chosen: torch.Tensor, weights: torch.Tensor, gate: torch.Tensor | None, experts: int, scale: float) -> None:
+def route_top(logits: GemmOut, chosen: torch.Tensor, weights: torch.Tensor, gate: torch.Tensor | None, experts: int, scale: float,
+              normalize: bool = True) -> None:
     """A learned router's choice from float logits [*, T, cols]: scores = sigmoid(logits[:, :experts]); ``chosen``
     [T, top] (int32) the ``top`` largest, ``weights`` [T, top] their scores over their sum (+ 1e-20) times ``scale``;
-    ``gate`` [T] = sigmoid(logits[:, experts]) where given (a shared expert's gate, one number per token)."""
+    ``gate`` [T] = sigmoid(logits[:, experts]) where given (a shared expert's gate, one number per token).  Without
+    ``normalize`` the weights are the chosen scores themselves times ``scale``."""
     tokens, top = chosen.shape
     _need(logits.tensor, "logits", torch.float32)
     _need(chosen, "chosen", torch.int32, (logits.rows, top))
@@ -946,7 +1023,7 @@ def route_top(logits: GemmOut, chosen: torch.Tensor, weights: torch.Tensor, gate
     if gate is not None:
         _need(gate, "gate", torch.float32, (tokens,))
     _call("experts", "qt_route_top", _ptr(logits.tensor), logits.n_splits, logits.split_stride, logits.cols, _ptr(chosen), _ptr(weights),
-          _ptr(gate), tokens, int(experts), top, float(scale), _stream())
+          _ptr(gate), tokens, int(experts), top, float(scale), 1 if normalize else 0, _stream())
 
 
 def _expert_extras(tokens: int, top: int, width: int, pair_weights, base: GemmOut | None, row_scale):
@@ -966,7 +1043,7 @@ def _expert_extras(tokens: int, top: int, width: int, pair_weights, base: GemmOu
 def experts_by_pair(x: torch.Tensor, token_ids: torch.Tensor | None, table: torch.Tensor, up: torch.Tensor, down: torch.Tensor,
                     mid: torch.Tensor, out: torch.Tensor, activation: str, pair_weight: float = 1.0,
                     pair_weights: torch.Tensor | None = None, gated: bool = False, limit: float = 0.0,
-                    base: GemmOut | None = None, row_scale: torch.Tensor | None = None) -> None:
+                    base: GemmOut | None = None, row_scale: torch.Tensor | None = None, in_weights: torch.Tensor | None = None) -> None:
     """out [T, width] (float) = pair_weight * sum over the ``top`` experts e that ``table[token_ids[t]]`` names of
     down[e] act(up[e] x[t]): one matrix-vector pass per (token, expert) pair, the form for few tokens.
     up [E, ff, width], down [E, width, ff], mid [T * top, ff] (scratch for the activations), all of x's element type.
@@ -974,11 +1051,14 @@ def experts_by_pair(x: torch.Tensor, token_ids: torch.Tensor | None, table: torc
     Without ``token_ids`` row t of ``table`` [T, top] names token t's experts (a router's choice).  ``pair_weights``
     [T, top] weighs every pair by itself.  ``gated``: up is [E, 2 ff, width], ff gate rows then ff up rows, and
     mid = act(gate) * up, or the capped gate with ``limit``.  ``base`` (float sums [*, T, width]) times
-    ``row_scale`` [T] is added to the result."""
+    ``row_scale`` [T] (1 without it) is added to the result.  ``in_weights`` [T, top]: a pair's expert reads its token's row
+    times the pair's weight (the weight on the input instead of the output)."""
     tokens, width = x.shape
     experts, ff = up.shape[0], up.shape[1] // (2 if gated else 1)
     top = table.shape[1]
     _need(x, "x")
+    if in_weights is not None:
+        _need(in_weights, "in_weights", torch.float32, (tokens, top))
     if token_ids is not None:
         _need(token_ids, "token_ids", torch.int32, (tokens,))
     _need(table, "table", torch.int32)
@@ -989,7 +1069,7 @@ def experts_by_pair(x: torch.Tensor, token_ids: torch.Tensor | None, table: torc
     weights_ptr, base_ptr, base_splits, base_stride, scale_ptr = _expert_extras(tokens, top, width, pair_weights, base, row_scale)
     _call("experts", "qt_experts_by_pair", _ptr(x), _ptr(token_ids), _ptr(table), _ptr(up), _ptr(down), _ptr(mid), _ptr(out),
           _code(x, "x"), tokens, table.shape[0], top, experts, width, ff, activation_code(activation, gated), float(pair_weight),
-          weights_ptr, 1 if gated else 0, float(limit), base_ptr, base_splits, base_stride, scale_ptr, _stream(), launches=2)
+          weights_ptr, 1 if gated else 0, float(limit), base_ptr, base_splits, base_stride, scale_ptr, _ptr(in_weights), _stream(), launches=2)
 
 
 EXPERT_TILE_ROWS = 128      # rows of one tile of the tiled expert products (the MMA's M)
@@ -1009,7 +1089,7 @@ def experts_tiled(x: torch.Tensor, token_ids: torch.Tensor | None, table: torch.
                   ordered: torch.Tensor, mid: torch.Tensor, y: torch.Tensor, route: torch.Tensor, out: torch.Tensor,
                   activation: str, pair_weight: float = 1.0, pair_weights: torch.Tensor | None = None, gated: bool = False,
                   limit: float = 0.0, wide: torch.Tensor | None = None, base: GemmOut | None = None,
-                  row_scale: torch.Tensor | None = None) -> None:
+                  row_scale: torch.Tensor | None = None, in_weights: torch.Tensor | None = None) -> None:
     """The same result as ``experts_by_pair`` for many tokens: the (token, expert) pairs are ordered by expert on the
     device, each expert's run padded to whole tiles of 128 rows, and both products run tile by tile on the tensor
     cores.  Scratch: ``ordered`` [rows, width], ``mid`` [rows, ff], ``y`` [rows, width] (bfloat16) with
@@ -1031,11 +1111,13 @@ def experts_tiled(x: torch.Tensor, token_ids: torch.Tensor | None, table: torch.
     _need(y, "y", torch.bfloat16, (rows, width))
     _need(route, "route", torch.int32, (tokens * top + rows + tiles,))
     _need(out, "out", torch.float32, (tokens, width))
+    if in_weights is not None:
+        _need(in_weights, "in_weights", torch.float32, (tokens, top))
     weights_ptr, base_ptr, base_splits, base_stride, scale_ptr = _expert_extras(tokens, top, width, pair_weights, base, row_scale)
     pair_row, row_token, tile_expert = route[:tokens * top], route[tokens * top:tokens * top + rows], route[tokens * top + rows:]
     status = _status_word(x.device)
     _call("experts", "qt_experts_route", _ptr(x), _ptr(token_ids), _ptr(table), _ptr(ordered), _ptr(pair_row), _ptr(row_token),
-          _ptr(tile_expert), tokens, table.shape[0], top, experts, width, EXPERT_TILE_ROWS, tiles, _stream(), launches=2)
+          _ptr(tile_expert), tokens, table.shape[0], top, experts, width, EXPERT_TILE_ROWS, tiles, _ptr(in_weights), _stream(), launches=2)
     if gated:
         _need(wide, "wide", torch.bfloat16, (rows, 2 * ff))
         _call("experts_tc", "qt_expert_gemm", _ptr(ordered), _ptr(up), _ptr(wide), BF16, _ptr(tile_expert), tiles, experts, 2 * ff, width,

@@ -3,7 +3,7 @@ from .base import (
     register_block, register_embedding, register_feed_forward, register_head, register_mixer, register_norm,
     register_position,
 )
-from . import attention, block, conv_attention, embedding, feed_forward, latent_attention, norm, position, recurrent  # noqa: F401  (register the built-in parts)
+from . import attention, block, conv_attention, embedding, feed_forward, latent_attention, norm, position, recurrent, side_by_side  # noqa: F401  (register the built-in parts)
 from .linear import Linear
 
 __all__ = [

@@ -26,7 +26,17 @@ Further parameters, each off unless given, for designs that treat scores or valu
   inside the root, no weight), times (1 - diff), with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff from four
   vectors of the layer (tensors ``names["lq1"]`` ...).  The projections' rows are reordered map-major when loaded,
   so that map m of head h is query head m * H + h and reads key head m * G + g; the value cache has G heads;
-* ``float_out``: the output projection hands on float sums (for a float residual addition).
+* ``float_out``: the output projection hands on float sums (for a float residual addition);
+* ``qk_norm`` = "unit": q and k heads are divided by their root mean square (``qk_norm_eps``) without a weight; a
+  rotation leaves a head's sum of squares as it is, so this is also the norm of a design that divides after rotating;
+  ``qk_norm`` = "whole": q and k are RMS-normed over all their heads at once, with weights of the projections' sizes;
+* ``keep_first`` (with ``window``): the first positions of a sequence stay visible to every later query, at their true
+  positions; the cache then keeps every key (no ring) and the kernels mask;
+* ``sink`` = "learned": the softmax's denominator also holds exp(s_h), one stored number per query head
+  (tensor ``names["sink"]``) that is not scaled and has no value; ``sink`` = True: the same with s_h = 0;
+* ``head_gate``: every head's output is multiplied by sigmoid(w_h . x), one number per head; the rows W_g [heads, hidden]
+  (tensor ``names["g"]``) ride at the end of the q/k/v projection, whose sums are then float (``float_proj`` asks for
+  float sums by itself).
 
 Values that are treated (``v_norm``, ``v_blend``, a head size of their own) go with no rotation and no q/k norm:
 bias, treatment and the cache write are then one kernel behind the projection (``kernels.qkv_treat_write``).
@@ -71,7 +81,17 @@ class Attention:
         self.scale = float(params.get("scale", self.d ** -0.5))
         self.window = params.get("window")
         self.own_kv = bool(params.get("own_kv", True))
-        self.qk_norm = bool(params.get("qk_norm", False))
+        self.norm_mode = {False: None, None: None, True: "head", "head": "head", "unit": "unit", "whole": "whole"}.get(params.get("qk_norm", False), "?")
+        if self.norm_mode == "?":
+            raise ValueError(f"{prefix}: qk_norm={params.get('qk_norm')!r} is none of False, True, 'unit', 'whole'")
+        self.qk_norm = self.norm_mode in ("head", "whole")          # norms that have weights
+        self.keep_first = int(params.get("keep_first") or 0) if params.get("window") else 0
+        self.sink = params.get("sink", False)
+        if self.sink not in (False, True, "learned"):
+            raise ValueError(f"{prefix}: sink={self.sink!r} is none of False, True, 'learned'")
+        self.head_gate = bool(params.get("head_gate", False))
+        self.float_proj = bool(params.get("float_proj", False)) or self.head_gate
+        self.sinks = None
         self.bias = bool(params.get("bias", False))        # q, k, v and o projections with a bias (attention.py:38-41)
         self.o_bias = bool(params.get("o_bias", self.bias))
         self.eps = float(params.get("qk_norm_eps", 1e-6))
@@ -96,20 +116,25 @@ class Attention:
         self.treated = self.v_norm_eps is not None or self.v_blend is not None or self.dv != self.d
         # values of their own shape that are otherwise untouched go with q/k norm and rotation (one kernel writes all)
         self.own_values = self.treated and self.v_norm_eps is None and self.v_blend is None and not self.bias
-        if self.maps > 1:
-            self.own_values = True
+        if self.maps > 1 or self.norm_mode in ("unit", "whole") or self.float_proj:
+            self.own_values = True            # the general kernel behind the projection
         if self.own_values:
             self.treated = False
         if self.treated and (self.qk_norm or not self.own_kv or position_spec.kind != "none"):
             raise ValueError(f"{prefix}: treated values (v_norm, v_blend) go with no rotation, no q/k norm and keys of the layer's own")
-        if self.maps > 1 and (self.bias or self.window or self.penalised):
-            raise ValueError(f"{prefix}: differential attention goes with no bias, window or distance penalty")
+        if self.maps > 1 and (self.bias or self.window or self.penalised or self.sink or self.head_gate or self.norm_mode in ("unit", "whole")):
+            raise ValueError(f"{prefix}: differential attention goes with no bias, window, distance penalty, sink, gate or norm of another kind")
+        if (self.keep_first or self.sink or self.head_gate or self.norm_mode in ("unit", "whole")) and (self.treated or self.bias or not self.own_kv or self.chunk):
+            raise ValueError(f"{prefix}: kept first keys, a sink, a gate per head and the unit and whole-row norms go with untreated values, "
+                             "no bias, no chunks and keys of the layer's own")
+        self.gate_cols = -(-self.heads_out // 8) * 8 if self.head_gate else 0       # the gate's rows, padded so that rows of sums stay aligned
         # the mma.sync attention kernels take values as wide as the keys (and compute the distance penalty, given a
         # positive scale); everything else goes to the generic kernels
         self.mma_scores = self.dv == self.d and (not self.penalised or self.scale > 0)
-        proj_rows = self.nq * self.d + ((self.nkv * self.d + self.v_heads * self.dv) if self.own_kv else 0)
+        proj_rows = self.nq * self.d + ((self.nkv * self.d + self.v_heads * self.dv) if self.own_kv else 0) + self.gate_cols
+        self.at_gate = proj_rows - self.gate_cols
         if self.own_values:
-            self.qkv = Linear("attn.qkv.own_values", proj_rows, self.hidden, runtime)
+            self.qkv = Linear("attn.qkv.own_values" + (".float" if self.float_proj else ""), proj_rows, self.hidden, runtime, float_out=self.float_proj)
         elif self.treated:
             self.qkv = Linear("attn.qkv.sums", proj_rows, self.hidden, runtime, float_out=True)      # float sums: the bias is added behind it
         else:
@@ -124,6 +149,8 @@ class Attention:
             ws.declare("attn.heads", runtime.max_step_tokens * self.heads_out * self.dv, runtime.dtype)
         ws.declare("attn.part_acc", _MAX_SPLIT_PAIRS * self.nq * self.dv, torch.float32)
         ws.declare("attn.part_ml", _MAX_SPLIT_PAIRS * self.nq * 2, torch.float32)
+        if self.norm_mode == "whole":
+            ws.declare("attn.row_inv", runtime.max_step_tokens * 2, torch.float32)
         self.side_name = "attn.values." + str(params.get("v_blend_key", "first"))
         if self.v_blend is not None:
             ws.declare(self.side_name, runtime.max_step_tokens * self.nkv * self.dv, torch.float32)
@@ -133,9 +160,10 @@ class Attention:
     # ------------------------------------------------------------------ weights
     @staticmethod
     def _names(params) -> dict[str, str]:
-        n = {k: params.get(k, k) for k in ("q", "k", "v", "o", "q_norm", "k_norm", "r1", "r2", "v_blend_weight", "lq1", "lk1", "lq2", "lk2")}
+        n = {k: params.get(k, k) for k in ("q", "k", "v", "o", "q_norm", "k_norm", "r1", "r2", "v_blend_weight", "lq1", "lk1", "lq2", "lk2", "sink", "g")}
         n["w"], n["b"] = str(params.get("weight_suffix", ".weight")), str(params.get("bias_suffix", ".bias"))
         n["nw"] = str(params.get("norm_suffix", ".weight"))
+        n["sink"] = str(params.get("sink_name", "sink"))          # ``sink`` itself says whether there is one
         return n
 
     @staticmethod
@@ -174,10 +202,15 @@ class Attention:
             # a source layer stores the weight too and never reads it; a layer outside the scheme may store it
             out[f"{prefix}.{n['v_blend_weight']}"] = TensorSpec((), role="vector", init_std=0.08, init_mean=0.4,
                                                                 optional=params.get("v_blend") != "blend")
-        if params.get("qk_norm", False):
-            out[f"{prefix}.{n['q_norm']}{n['nw']}"] = TensorSpec((d,), role="vector", init_std=0.1, init_mean=1.0)
+        if params.get("qk_norm", False) in (True, "head", "whole"):
+            whole = params.get("qk_norm") == "whole"
+            out[f"{prefix}.{n['q_norm']}{n['nw']}"] = TensorSpec((nq * d if whole else d,), role="vector", init_std=0.1, init_mean=1.0)
             if own_kv:
-                out[f"{prefix}.{n['k_norm']}{n['nw']}"] = TensorSpec((d,), role="vector", init_std=0.1, init_mean=1.0)
+                out[f"{prefix}.{n['k_norm']}{n['nw']}"] = TensorSpec((nkv * d if whole else d,), role="vector", init_std=0.1, init_mean=1.0)
+        if params.get("sink", False) == "learned":
+            out[f"{prefix}.{n['sink']}"] = TensorSpec((nq,), role="vector", init_std=1.0, init_mean=0.0)
+        if params.get("head_gate", False):
+            out[f"{prefix}.{n['g']}{n['w']}"] = TensorSpec((nq, hidden), init_std=std)
         return out
 
     def load(self, source) -> None:
@@ -195,6 +228,11 @@ class Attention:
             # one number for the layer, made once on the host (the same bits wherever the tensors were drawn)
             vec = {name: source(f"{p}.{n[name]}").double().cpu() for name in ("lq1", "lk1", "lq2", "lk2")}
             self.lam = float(torch.exp((vec["lq1"] * vec["lk1"]).sum()) - torch.exp((vec["lq2"] * vec["lk2"]).sum())) + self.diff
+        if self.head_gate:
+            gate = source(f"{p}.{n['g']}{n['w']}")
+            rows += [gate, torch.zeros(self.gate_cols - gate.shape[0], self.hidden, dtype=gate.dtype, device=gate.device)]
+        if self.sink == "learned":
+            self.sinks = to_device(source(f"{p}.{n['sink']}"), torch.float32, self.runtime.device)
         self.qkv.set_weight(torch.cat([r.to(self.runtime.dtype) for r in rows], dim=0))
         self.o.set_weight(source(f"{p}.{n['o']}{n['w']}"))
         if self.bias:
@@ -223,7 +261,7 @@ class Attention:
 
     # ------------------------------------------------------------------ cache
     def cache_request(self) -> KVRequest | None:
-        return KVRequest(self.nkv, self.d, self.window, self.dv if self.dv != self.d else None,
+        return KVRequest(self.nkv, self.d, None if self.keep_first else self.window, self.dv if self.dv != self.d else None,
                          self.v_heads if self.v_heads != self.nkv else None)
 
     # ------------------------------------------------------------------ run
@@ -237,7 +275,7 @@ class Attention:
         two tiles of 32 keys.  The generic kernel (other element types and head sizes) takes one range per
         block: the count whose blocks fill whole waves of three blocks per SM nearly as well as the best one.
         """
-        span = ctx.max_context if not self.window else min(ctx.max_context, self.window)
+        span = ctx.max_context if not self.window else min(ctx.max_context, self.window + self.keep_first)
         if self.chunk:
             span = min(span, self.chunk)
         group = self.nq // self.nkv
@@ -311,22 +349,27 @@ class Attention:
                               table if write else None, self.q_weight, self.k_weight, self.eps, self.cos_sin, self.nq, self.nkv,
                               self.d, cache.page_tokens, cache.ring_tokens, write_kv=write, interleaved=self.interleaved)
         else:
+            proj = self.qkv(x)
             kernels.qk_norm_rope_write(
-                self.qkv(x), q, cache.k if write else None, cache.v if write else None, ctx.token_seq, ctx.token_pos,
+                proj, q, cache.k if write else None, cache.v if write else None, ctx.token_seq, ctx.token_pos,
                 table if write else None, self.q_weight, self.k_weight, self.eps, self.cos_sin, self.nq, self.nkv, self.d,
                 cache.page_tokens, cache.ring_tokens, write_kv=write, kv_in_proj=self.own_kv, interleaved=self.interleaved,
-                v_heads=self.v_heads if self.own_values else None, v_head_dim=self.dv if self.own_values else None)
+                v_heads=self.v_heads if self.own_values else None, v_head_dim=self.dv if self.own_values else None,
+                unit_norm=self.norm_mode == "unit", row_inv=ws.view("attn.row_inv", tokens, 2) if self.norm_mode == "whole" else None,
+                extra_cols=self.gate_cols)
         if ctx.is_decode:
             n_splits, warps = self._splits(ctx, cache)
             kernels.attention_decode(q, cache.k, cache.v, out, table, ctx.seq_len, self.nkv, cache.page_tokens,
                                      cache.ring_tokens, self.window, self.scale, n_splits,
                                      ws.view("attn.part_acc", _MAX_SPLIT_PAIRS * self.nq * self.dv),
                                      ws.view("attn.part_ml", _MAX_SPLIT_PAIRS * self.nq * 2), warps=warps, penalty=penalty,
-                                     chunk=self.chunk)
+                                     chunk=self.chunk, keep_first=self.keep_first, sink=bool(self.sink), sinks=self.sinks)
         else:
             kernels.attention_prefill(q, cache.k, cache.v, out, table, ctx.seq_start, ctx.seq_past, ctx.max_q_len,
                                       self.nkv, cache.page_tokens, cache.ring_tokens, self.window, self.scale, penalty=penalty,
-                                      chunk=self.chunk)
+                                      chunk=self.chunk, keep_first=self.keep_first, sink=bool(self.sink), sinks=self.sinks)
+        if self.head_gate:
+            kernels.gate_mul(out.view(tokens, self.nq * self.dv), proj, self.at_gate, group=self.dv)
         if self.maps > 1:
             heads = ws.view("attn.heads", tokens, self.heads_out, self.dv)
             kernels.map_difference(out, heads, self.lam, self.head_norm_eps, 1.0 - self.diff)

@@ -248,6 +248,11 @@ class RoutedExperts:
     ``shared`` (a dict: ``intermediate_size``, ``limit``) a further expert of the same form runs for every token and is
     added, times sigmoid(w_gate . h), one number per token; its gate is one more row of the router's product.
 
+    ``normalize`` = False: the weights are the chosen scores themselves (times ``route_scale``), not divided by their sum.
+    ``weight_on`` = "input": a pair's weight multiplies what its expert reads, not what it returns: the output is the sum of
+    expert_e(w_e h), which for a gated expert is another function of w_e.  ``shared_gated`` = False: the shared expert is
+    added as it is, without a gate (and without the router's extra row).
+
     The routing is computed on the device by a kernel behind the router's product, so a step launches the same
     kernels whatever the tokens are.  Few (token, expert) pairs run as matrix-vector passes per pair, many are
     ordered by expert and run in tiles on the tensor cores (``experts.cu``, ``experts_tc.cu``), as for experts chosen
@@ -275,6 +280,11 @@ class RoutedExperts:
             raise ValueError(f"{prefix}: gate activation {self.activation!r} is not one of {sorted(kernels.ACTIVATIONS) + [kernels.CAPPED_GATE]}")
         if not 0 < self.top <= self.experts:
             raise ValueError(f"{prefix}: {self.top} experts per token out of {self.experts}")
+        self.normalize = bool(params.get("normalize", True))
+        self.weight_on = str(params.get("weight_on", "output"))
+        if self.weight_on not in ("output", "input"):
+            raise ValueError(f"{prefix}: weight_on={self.weight_on!r} is neither 'output' nor 'input'")
+        self.shared_gated = bool(params.get("shared_gated", True))
         shared = params.get("shared")
         self.shared = None
         if shared is not None:
@@ -284,7 +294,7 @@ class RoutedExperts:
                                     "weight_suffix": params.get("weight_suffix", ".weight"), "float_out": True, "buffers": "experts.shared",
                                     "init_std": float(params.get("init_std", 0.02))},
                                    f"{prefix}.{params.get('shared_name', 'shared')}", runtime)
-        self.router = Linear("experts.router", self.experts + (1 if self.shared else 0), self.hidden, runtime, float_out=True)
+        self.router = Linear("experts.router", self.experts + (1 if self.shared and self.shared_gated else 0), self.hidden, runtime, float_out=True)
         self.up = self.down = None
         ws = runtime.workspace
         tokens = runtime.max_step_tokens
@@ -329,7 +339,8 @@ class RoutedExperts:
                    "up": params.get("up", "up"), "down": params.get("down", "down"), "weight_suffix": params.get("weight_suffix", ".weight"),
                    "init_std": std}
             out.update(GatedMLP.expected_tensors(sub, f"{prefix}.{params.get('shared_name', 'shared')}"))
-            out[shared_gate] = TensorSpec((1, hidden), init_std=float(params.get("router_init_std", 0.1)))
+            if params.get("shared_gated", True):
+                out[shared_gate] = TensorSpec((1, hidden), init_std=float(params.get("router_init_std", 0.1)))
         return out
 
     def load(self, source) -> None:
@@ -340,7 +351,8 @@ class RoutedExperts:
         rows = [source(router).to(dtype)]
         if self.shared is not None:
             self.shared.load(source)
-            rows.append(source(shared_gate).to(dtype).reshape(1, self.hidden))
+            if self.shared_gated:
+                rows.append(source(shared_gate).to(dtype).reshape(1, self.hidden))
         self.router.set_weight(torch.cat(rows, dim=0))
 
     def forward(self, x, ctx) -> GemmOut:
@@ -349,8 +361,10 @@ class RoutedExperts:
         out = ws.view("experts.out", tokens, self.hidden)
         chosen = ws.view("experts.chosen", tokens, self.top)
         weights = ws.view("experts.weights", tokens, self.top)
-        gate = ws.view("experts.shared_gate", tokens) if self.shared is not None else None
-        kernels.route_top(self.router(x), chosen, weights, gate, self.experts, self.route_scale)
+        gate = ws.view("experts.shared_gate", tokens) if self.shared is not None and self.shared_gated else None
+        kernels.route_top(self.router(x), chosen, weights, gate, self.experts, self.route_scale, self.normalize)
+        on_input = self.weight_on == "input"
+        out_weights, in_weights = (None, weights) if on_input else (weights, None)
         base = None
         if self.shared is not None:
             base = self.shared.forward(x, ctx)
@@ -361,9 +375,11 @@ class RoutedExperts:
             rows = tiles * kernels.EXPERT_TILE_ROWS
             kernels.experts_tiled(x, None, chosen, self.up, self.down, ws.view("experts.ordered", rows, self.hidden),
                                   ws.view("experts.mid", rows, self.inter), ws.view("experts.y", rows, self.hidden),
-                                  ws.view("experts.route", pairs + rows + tiles), out, self.activation, pair_weights=weights, gated=True,
-                                  limit=self.limit, wide=ws.view("experts.wide", rows, 2 * self.inter), base=base, row_scale=gate)
+                                  ws.view("experts.route", pairs + rows + tiles), out, self.activation, pair_weight=1.0, pair_weights=out_weights,
+                                  gated=True, limit=self.limit, wide=ws.view("experts.wide", rows, 2 * self.inter), base=base, row_scale=gate,
+                                  in_weights=in_weights)
         else:
             kernels.experts_by_pair(x, None, chosen, self.up, self.down, ws.view("experts.mid", pairs, self.inter), out, self.activation,
-                                    pair_weights=weights, gated=True, limit=self.limit, base=base, row_scale=gate)
+                                    pair_weight=1.0, pair_weights=out_weights, gated=True, limit=self.limit, base=base, row_scale=gate,
+                                    in_weights=in_weights)
         return GemmOut(out.view(1, tokens, self.hidden))

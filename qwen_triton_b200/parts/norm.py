@@ -136,10 +136,11 @@ class DynamicTanh:
 
 @register_norm("layernorm")
 class LayerNorm:
-    """y = (x - mean) / sqrt(var + eps) * w over the row, the variance being the mean of the squared deviations; a weight
-    and no bias.  Parameters: ``size``, ``eps``, ``suffix`` (what the weight's tensor name adds to the norm's name,
-    default ".weight") and ``scale`` (default 1): a constant that multiplies the weight when it is loaded, for a model
-    whose logits are the head's product times a constant (the product is linear, so the factor may ride on its input).
+    """y = (x - mean) / sqrt(var + eps) * w (+ b) over the row, the variance being the mean of the squared deviations.
+    Parameters: ``size``, ``eps``, ``suffix`` (what the weight's tensor name adds to the norm's name, default ".weight"),
+    ``bias_suffix`` (the same for a bias; absent: the norm has none) and ``scale`` (default 1): a constant that multiplies
+    weight and bias when they are loaded, for a model whose logits are the head's product times a constant (the product
+    is linear, so the factor may ride on its input) or whose sublayers are added to the stream times a constant.
 
     ``folds_post_norm``: where the stream's pending addition is to pass a norm of its own first (``stream.post``, another
     norm of this kind: a layer that norms what a sublayer returns before adding it), the same launch norms the addition,
@@ -154,19 +155,27 @@ class LayerNorm:
         self.eps = float(params["eps"])
         self.scale = float(params.get("scale", 1.0))
         self.tensor = name + str(params.get("suffix", ".weight"))
+        self.bias_tensor = name + str(params["bias_suffix"]) if params.get("bias_suffix") is not None else None
         self.name = name
         self.runtime = runtime
         self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
         runtime.workspace.declare("normed", runtime.max_step_tokens * self.size, runtime.dtype)
 
     @classmethod
     def expected_tensors(cls, params, name: str) -> dict[str, TensorSpec]:
-        return {name + str(params.get("suffix", ".weight")): TensorSpec((int(params["size"]),), role="vector", init_std=0.1, init_mean=1.0)}
+        out = {name + str(params.get("suffix", ".weight")): TensorSpec((int(params["size"]),), role="vector", init_std=0.1, init_mean=1.0)}
+        if params.get("bias_suffix") is not None:
+            out[name + str(params["bias_suffix"])] = TensorSpec((int(params["size"]),), role="vector", init_std=0.1, init_mean=0.0)
+        return out
 
     def load(self, source) -> None:
         self.weight = to_device(source(self.tensor), torch.float32, self.runtime.device)
+        if self.bias_tensor is not None:
+            self.bias = to_device(source(self.bias_tensor), torch.float32, self.runtime.device)
         if self.scale != 1.0:
             self.weight = self.weight * self.scale
+            self.bias = self.bias * self.scale if self.bias is not None else None
 
     def apply(self, stream: ResidualStream, rows: torch.Tensor | None = None, lazy: bool = False):
         if stream.more:
@@ -178,7 +187,47 @@ class LayerNorm:
             raise RuntimeError(f"{self.name}: the pending addition's own norm has eps={post.eps}, this one {self.eps}")
         count = stream.residual.shape[0] if rows is None else rows.shape[0]
         out = self.runtime.workspace.view("normed", count, self.size)
-        kernels.add_layernorm(stream.residual, stream.pending, post.weight if post is not None else None, self.weight, self.eps, out, rows)
+        kernels.add_layernorm(stream.residual, stream.pending, post.weight if post is not None else None, self.weight, self.eps, out, rows,
+                              post_bias=post.bias if post is not None else None, bias=self.bias)
+        if rows is None:
+            stream.pending = None
+            stream.post = None
+        return out
+
+
+@register_norm("none")
+class NoNorm:
+    """No norm: a sublayer that reads the stream itself.  ``apply`` folds the pending addition into the stream (after the
+    addition's own layer norm where it has one, ``stream.post``: ``folds_post_norm``) and returns the stream's rows in the
+    activation type.  Parameter: ``size``.  It has no tensors."""
+
+    graph_safe = True
+    offers_scaled_rows = False
+    folds_post_norm = True
+
+    def __init__(self, params, name: str, runtime: Runtime) -> None:
+        self.size = int(params["size"])
+        self.name = name
+        self.runtime = runtime
+        runtime.workspace.declare("normed", runtime.max_step_tokens * self.size, runtime.dtype)
+
+    @classmethod
+    def expected_tensors(cls, params, name: str) -> dict[str, TensorSpec]:
+        return {}
+
+    def load(self, source) -> None:
+        pass
+
+    def apply(self, stream: ResidualStream, rows: torch.Tensor | None = None, lazy: bool = False):
+        if stream.more:
+            raise RuntimeError(f"{self.name}: one pending addition is folded here; the stream holds {1 + len(stream.more)}")
+        post = stream.post
+        if post is not None and not isinstance(post, LayerNorm):
+            raise RuntimeError(f"{self.name}: the pending addition's own norm is not a layer norm")
+        count = stream.residual.shape[0] if rows is None else rows.shape[0]
+        out = self.runtime.workspace.view("normed", count, self.size)
+        kernels.add_layernorm(stream.residual, stream.pending, post.weight if post is not None else None, None,
+                              post.eps if post is not None else 1e-6, out, rows, post_bias=post.bias if post is not None else None)
         if rows is None:
             stream.pending = None
             stream.post = None

@@ -87,6 +87,49 @@ class YarnRotaryTable:
         return (torch.cat((angles.cos(), angles.sin()), dim=-1) * self.magnitude).to(torch.float32).contiguous().to(self.runtime.device)
 
 
+@register_position("rope_wavelength")
+class WavelengthRotaryTable:
+    """Rotary angles whose frequencies are stretched by wavelength: with f_i = theta^(-2i/rd) and wavelength l_i = 2 pi / f_i,
+    a pair with l_i < original / high keeps f_i, one with l_i > original / low turns at f_i / factor, and the pairs between
+    blend the two, (1 - s) f_i / factor + s f_i with s = (original / l_i - low) / (high - low).  Without ``factor`` the
+    rotation is plain.  Frequencies and angles are formed in float64, cos and sin rounded once to float.  Parameters:
+    ``theta``, ``rotary_dim``, ``head_dim``, and optionally ``factor``, ``low``, ``high``, ``original``."""
+
+    interleaved = False
+
+    def __init__(self, params, runtime: Runtime) -> None:
+        self.theta = float(params["theta"])
+        self.rotary_dim = int(params["rotary_dim"])
+        if self.rotary_dim % 2 or self.rotary_dim <= 0 or self.rotary_dim > int(params["head_dim"]):
+            raise ValueError(f"rotary_dim={self.rotary_dim} must be even and within head_dim={params['head_dim']}")
+        self.scaling = None
+        if params.get("factor") is not None:
+            self.scaling = tuple(float(params[key]) for key in ("factor", "low", "high", "original"))
+            factor, low, high, original = self.scaling
+            if factor <= 0 or original <= 0 or low <= 0 or high <= low:
+                raise ValueError("stretched rotation needs positive factor, original and low, and high above low")
+        self.runtime = runtime
+
+    def key(self) -> tuple:
+        return ("rope_wavelength", self.theta, self.rotary_dim, self.scaling)
+
+    def frequencies(self) -> torch.Tensor:
+        import math
+        plain = self.theta ** (-torch.arange(self.rotary_dim // 2, dtype=torch.float64) * 2.0 / self.rotary_dim)
+        if self.scaling is None:
+            return plain
+        factor, low, high, original = self.scaling
+        wavelength = 2.0 * math.pi / plain
+        blend = ((original / wavelength - low) / (high - low))
+        mixed = (1.0 - blend) * plain / factor + blend * plain
+        return torch.where(wavelength < original / high, plain, torch.where(wavelength > original / low, plain / factor, mixed))
+
+    def table(self, max_positions: int) -> torch.Tensor:
+        """float32 [max_positions, rotary_dim]: cos in the first half of each row, sin in the second."""
+        angles = torch.arange(max_positions, dtype=torch.float64)[:, None] * self.frequencies()[None, :]
+        return torch.cat((angles.cos(), angles.sin()), dim=-1).to(torch.float32).contiguous().to(self.runtime.device)
+
+
 @register_position("none")
 class NoPosition:
     def __init__(self, params, runtime: Runtime) -> None:

@@ -172,3 +172,104 @@ class GatedDeltaRule:
         normed = normed.view(tokens, self.heads * self.vdim)
         # few tokens: the product is left to the block, which launches it with the residual addition in its epilogue
         return DeferredProduct(self.o, normed) if self.o.fusable(tokens) else self.o(normed)
+
+
+@register_mixer("linear_attention")
+class LinearAttention:
+    """Linear attention with a constant decay per head ("lightning attention"):
+
+        S <- decay_h S + k_t v_t^T;   o_t = S^T q_t
+
+    with q = act(W_q h), k = act(W_k h) ([heads, dim]) and v = act(W_v h) ([heads, vdim]), act = SiLU (``activation``: "silu"
+    or "none"), no other scale.  The heads' outputs of a token are RMS-normed together (one mean over all heads x vdim
+    elements, ``eps`` inside the root) with a weight of that size, multiplied by sigmoid(W_g h) (``gate``) and projected by
+    W_o.  Per sequence the mixer keeps the states, float, zero for a new sequence, in the cache's per-slot state rows
+    (stored transposed, [heads, vdim, dim]).  The four projections of h run as one product with float sums; SiLU, the
+    recurrence, the norm and the gate are float (``csrc/linear_attention.cu``).
+
+    Parameters: ``hidden_size``, ``num_heads``, ``head_dim``, ``v_head_dim``, ``decay`` (one number per head), ``eps``,
+    ``activation``, ``gate``, ``float_out``, ``init_std``, and the tensor-name pieces ``q``, ``k``, ``v``, ``g``, ``o``, ``norm``,
+    ``weight_suffix``."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix: str, runtime: Runtime) -> None:
+        self.prefix, self.runtime, self.params = prefix, runtime, dict(params)
+        self.hidden = int(params["hidden_size"])
+        self.heads = int(params["num_heads"])
+        self.dim = int(params["head_dim"])
+        self.vdim = int(params.get("v_head_dim") or self.dim)
+        self.eps = float(params.get("eps", 1e-6))
+        self.gated = bool(params.get("gate", True))
+        activation = params.get("activation", "silu")
+        if activation not in ("silu", "none"):
+            raise ValueError(f"{prefix}: activation {activation!r} on q, k and v (silu or none)")
+        self.act = activation == "silu"
+        decay = [float(d) for d in params["decay"]]
+        if len(decay) != self.heads:
+            raise ValueError(f"{prefix}: {len(decay)} decays for {self.heads} heads")
+        if self.dim > kernels.LINEAR_ATTENTION_MAX_DIM:
+            raise ValueError(f"{prefix}: {self.dim} key channels per head are beyond what the recurrence kernel holds "
+                             f"({kernels.LINEAR_ATTENTION_MAX_DIM})")
+        self.decay_values = decay
+        self.decay = None
+        self.at_k = self.heads * self.dim
+        self.at_v = 2 * self.heads * self.dim
+        self.at_gate = self.at_v + self.heads * self.vdim
+        used = self.at_gate + (self.heads * self.vdim if self.gated else 0)
+        self.proj_rows = -(-used // 8) * 8
+        self.proj = Linear("linattn.proj", self.proj_rows, self.hidden, runtime, float_out=True)
+        float_out = bool(params.get("float_out", False))
+        self.o = Linear("linattn.o" + (".float" if float_out else ""), self.hidden, self.heads * self.vdim, runtime, float_out=float_out, role="attn_out")
+        ws = runtime.workspace
+        ws.declare("linattn.read", runtime.max_step_tokens * self.heads * self.vdim, torch.float32)
+        ws.declare("linattn.normed", runtime.max_step_tokens * self.heads * self.vdim, runtime.dtype)
+        self.norm = None
+
+    @staticmethod
+    def _names(params, prefix: str) -> dict[str, str]:
+        w = str(params.get("weight_suffix", ".weight"))
+        n = {key: f"{prefix}.{params.get(key, key)}{w}" for key in ("q", "k", "v", "g", "o")}
+        n["norm"] = f"{prefix}.{params.get('norm', 'norm')}"
+        return n
+
+    @classmethod
+    def expected_tensors(cls, params, prefix: str) -> dict[str, TensorSpec]:
+        hidden, heads, dim = int(params["hidden_size"]), int(params["num_heads"]), int(params["head_dim"])
+        vdim = int(params.get("v_head_dim") or dim)
+        n = cls._names(params, prefix)
+        std = float(params.get("init_std", 0.02))
+        out = {n["q"]: TensorSpec((heads * dim, hidden), init_std=std), n["k"]: TensorSpec((heads * dim, hidden), init_std=std),
+               n["v"]: TensorSpec((heads * vdim, hidden), init_std=std), n["o"]: TensorSpec((hidden, heads * vdim), init_std=std),
+               n["norm"]: TensorSpec((heads * vdim,), role="vector", init_std=0.1, init_mean=1.0)}
+        if params.get("gate", True):
+            out[n["g"]] = TensorSpec((heads * vdim, hidden), init_std=std)
+        return out
+
+    def load(self, source) -> None:
+        n = self._names(self.params, self.prefix)
+        dtype, device = self.runtime.dtype, self.runtime.device
+        rows = [source(n[key]).to(dtype) for key in (("q", "k", "v", "g") if self.gated else ("q", "k", "v"))]
+        used = sum(r.shape[0] for r in rows)
+        if self.proj_rows > used:
+            rows.append(torch.zeros(self.proj_rows - used, self.hidden, dtype=dtype, device=rows[0].device))
+        self.proj.set_weight(torch.cat(rows, dim=0))
+        self.o.set_weight(source(n["o"]))
+        self.norm = to_device(source(n["norm"]), torch.float32, device)
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=device)
+
+    def cache_request(self):
+        return StateRequest((self.heads, self.vdim, self.dim), torch.float32)
+
+    def forward(self, x, ctx, cache):
+        if not cache.writable:
+            raise ValueError(f"{self.prefix}: a recurrent mixer cannot read another layer's state")
+        tokens = x.shape[0]
+        ws = self.runtime.workspace
+        proj = self.proj(x)
+        read = ws.view("linattn.read", tokens, self.heads, self.vdim)
+        kernels.linear_attention_scan(proj, 0, self.at_k, self.at_v, self.decay, cache.state, read, ctx, self.dim, self.act)
+        normed = ws.view("linattn.normed", tokens, self.heads * self.vdim)
+        kernels.linear_attention_gate_norm(read.view(tokens, self.heads * self.vdim), proj if self.gated else None, self.at_gate, self.norm,
+                                           self.eps, 1.0, normed)
+        return self.o(normed)
