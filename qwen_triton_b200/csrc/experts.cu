@@ -283,8 +283,8 @@ __global__ void expert_combine_kernel(const T* __restrict__ y, const int* __rest
 }
 
 // A learned router's choice.  logits [splits, T, cols] float (column e < experts: expert e; column `experts`, if
-// shared_gate, the logit of a shared expert's gate).  Scores are sigmoid(logit); the `top` largest are chosen (of equal
-// scores the lower expert first), their weights are the scores over their sum (+ 1e-20) times `scale`, or, without `normalize`, the scores themselves times `scale`.
+// shared_gate, the logit of a shared expert's gate).  Scores are sigmoid(logit); the `top` largest are chosen (by their
+// logits; of equal ones the lower expert first), their weights are the scores over their sum (+ 1e-20) times `scale`, or, without `normalize`, the scores themselves times `scale`.
 // One warp per token; chosen [T, top], weights [T, top], gate [T] = sigmoid of the extra column.
 __global__ void __launch_bounds__(128) route_top_kernel(const float* __restrict__ logits, int n_splits, size_t split_stride, int cols,
                                                         int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ gate,
@@ -295,23 +295,25 @@ __global__ void __launch_bounds__(128) route_top_kernel(const float* __restrict_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + warp;
     if (t >= n_tokens) return;
-    float* score = route_scores + (size_t)warp * experts;
-    for (int e = lane; e < experts; e += 32) score[e] = 1.f / (1.f + expf(-load_sum(logits, (size_t)t * cols + e, n_splits, split_stride)));
+    float* score = route_scores + (size_t)warp * experts;        // the logits: their order is the scores' order, and two logits
+    // that differ stay apart where their sigmoids round to the same float
+    for (int e = lane; e < experts; e += 32) score[e] = load_sum(logits, (size_t)t * cols + e, n_splits, split_stride);
     if (gate && lane == 0) gate[t] = 1.f / (1.f + expf(-load_sum(logits, (size_t)t * cols + experts, n_splits, split_stride)));
     __syncwarp();
     float sum = 0.f;
     for (int k = 0; k < top; ++k) {
-        float best = -1.f;
+        float best = -INFINITY;
         int at = experts;
         for (int e = lane; e < experts; e += 32)
-            if (score[e] > best) { best = score[e]; at = e; }
+            if (score[e] > best || at == experts) { best = score[e]; at = e; }
         for (int off = 16; off > 0; off >>= 1) {
             const float other = __shfl_xor_sync(0xffffffffu, best, off);
             const int where = __shfl_xor_sync(0xffffffffu, at, off);
-            if (other > best || (other == best && where < at)) { best = other; at = where; }
+            if (where < experts && (at == experts || other > best || (other == best && where < at))) { best = other; at = where; }
         }
-        sum += best;
-        if (lane == 0) { chosen[(size_t)t * top + k] = at; weights[(size_t)t * top + k] = best; score[at] = -2.f; }
+        const float chosen_score = 1.f / (1.f + expf(-best));
+        sum += chosen_score;
+        if (lane == 0) { chosen[(size_t)t * top + k] = at; weights[(size_t)t * top + k] = chosen_score; score[at] = -INFINITY; }
         __syncwarp();
     }
     if (lane < top) {

@@ -157,12 +157,19 @@ def expert(h, t, prefix):
     return (silu(h @ t[prefix + ".gate"].T) * (h @ t[prefix + ".up"].T)) @ t[prefix + ".down"].T
 
 
-def routed_feed_forward(h, t, prefix, mlp):
+def routed_feed_forward(h, t, prefix, mlp, margins: list | None = None):
+    """``margins`` collects, per position, how clear the router's choice is: the gap between the last chosen logit and the
+    first one left out, over the root mean square of the position's logits (infinite where every expert is chosen)."""
     experts, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
-    scores = torch.sigmoid(h @ t[prefix + ".router"].T)
+    logits = h @ t[prefix + ".router"].T
+    scores = torch.sigmoid(logits)
+    if margins is not None:
+        ordered = logits.sort(dim=-1, descending=True).values
+        gap = ordered[:, top - 1] - ordered[:, top] if top < experts else torch.full((h.shape[0],), math.inf, dtype=F)
+        margins.append(gap / (logits.pow(2).mean(-1).sqrt() + 1e-30))
     out = torch.zeros_like(h)
     for row in range(h.shape[0]):
-        order = sorted(range(experts), key=lambda e: (-float(scores[row, e]), e))[:top]
+        order = sorted(range(experts), key=lambda e: (-float(logits[row, e]), e))[:top]      # the scores' order is the logits' order
         for e in order:
             out[row] += expert(scores[row, e] * h[row], t, f"{prefix}.e{e}")
     if mlp.get("shared") is not None:
@@ -170,8 +177,9 @@ def routed_feed_forward(h, t, prefix, mlp):
     return out
 
 
-def forward(config, tensors, tokens, layers_out: list | None = None):
-    """Logits [T, vocab] of one sequence from its start; ``layers_out`` collects the stream after every layer run."""
+def forward(config, tensors, tokens, layers_out: list | None = None, margins: list | None = None):
+    """Logits [T, vocab] of one sequence from its start; ``layers_out`` collects the stream after every layer run,
+    ``margins`` the clearness of every router's choice per position (see ``routed_feed_forward``)."""
     t = {name: value.to(F) for name, value in tensors.items()}
     eps = float(config["norm"]["eps"])
     mult = float(config.get("residual_mult", 1.0))
@@ -182,7 +190,7 @@ def forward(config, tensors, tokens, layers_out: list | None = None):
         mixer = attention_mixer if entry["type"] == "attention" else parallel_mixer
         x = x + mult * layer_norm(mixer(x, t, p + ".mix", entry["mixer"], eps), t[p + ".norm1"], t[p + ".norm1.b"], eps)
         if entry.get("mlp") is not None:
-            x = x + mult * layer_norm(routed_feed_forward(x, t, p + ".mlp", entry["mlp"]), t[p + ".norm2"], t[p + ".norm2.b"], eps)
+            x = x + mult * layer_norm(routed_feed_forward(x, t, p + ".mlp", entry["mlp"], margins), t[p + ".norm2"], t[p + ".norm2.b"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
     x = layer_norm(x, t["final.norm"], t["final.norm.b"], eps)
