@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the Qwen3-8B shape on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl b200|reference] [--temperature T]
-    python bench.py --workload 0.6b-unequal | 32b-long | lederax-layers | vunepel-layers | bisodra-layers
+    python bench.py --workload 0.6b-unequal | 32b-long | lederax-layers | vunepel-layers | bisodra-layers | regupel-layers
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 from a 2,048-token cache,
 timed on the device over the decode steps (step function plus greedy sampling kernel, tokens given
@@ -24,7 +24,10 @@ Vunepel design: differential attention with a dense feed-forward, two gated-delt
 attention layer that reads the first one's keys and values; ``--size``, ``--arm`` and ``--phase`` run one of its
 measurements alone, for a profiler), ``bisodra-layers`` (the same for four layers of the Bisodra design: attention through
 a latent, attention with a short convolution on q and k under a window with kept first keys, a latent layer that reads the
-first one's cache rows, a second convolution layer; the same three options).
+first one's cache rows, a second convolution layer; the same three options), ``regupel-layers`` (four layers of the Regupel
+design: two parallel layers, windowed attention with kept first keys beside a linear attention with a decay per head, and two
+attention layers with a sink and a gate per head, each with routed experts and a shared expert, beside the Vunepel layers
+of equal size; the same three options).
 """
 from __future__ import annotations
 
@@ -58,9 +61,9 @@ def parse_args():
     parser.add_argument("--no-prefill", action="store_true")
     parser.add_argument("--min-seconds", type=float, default=2.0, help="a timed region lasts at least this long")
     parser.add_argument("--temperature", type=float, default=0.0, help="sampling temperature of the end-to-end run (0: greedy)")
-    parser.add_argument("--workload", default=None, choices=["0.6b-unequal", "32b-long", "lederax-layers", "vunepel-layers", "bisodra-layers"])
+    parser.add_argument("--workload", default=None, choices=["0.6b-unequal", "32b-long", "lederax-layers", "vunepel-layers", "bisodra-layers", "regupel-layers"])
     parser.add_argument("--size", default=None, help="vunepel-layers, bisodra-layers: only the size whose name starts with this")
-    parser.add_argument("--arm", default=None, choices=["vunepel", "bisodra", "dense"], help="vunepel-layers, bisodra-layers: only this model")
+    parser.add_argument("--arm", default=None, choices=["vunepel", "bisodra", "regupel", "dense"], help="vunepel-layers, bisodra-layers, regupel-layers: only this model")
     parser.add_argument("--phase", default=None, choices=["prefill", "decode8", "decode64"], help="vunepel-layers, bisodra-layers: only this measurement")
     return parser.parse_args()
 
@@ -428,6 +431,126 @@ def run_bisodra_layers(args) -> dict:
             "sizes": out}
 
 
+REGUPEL_SIZES = (
+    # name, width, attention heads, kv heads, head size (keys and values), window, kept first keys, rotated elements,
+    # linear-attention heads, key size, value size, experts, top, expert width, shared width
+    ("w2048-h16x128-win1024-lin16x128-e16x1024-top2", 2048, 16, 4, 128, 1024, 64, 64, 16, 128, 128, 16, 2, 1024, 1024),
+    ("w4096-h32x128-win4096-lin32x128-e16x2048-top2", 4096, 32, 8, 128, 4096, 128, 64, 32, 128, 128, 16, 2, 2048, 2048),
+    ("w1024-h8x64-win512-lin8x64-e8x2048-top1", 1024, 8, 8, 64, 512, 16, 32, 8, 64, 128, 8, 1, 2048, 1024),
+)
+
+
+def run_regupel_layers(args) -> dict:
+    """Prefill and one-token steps of four Regupel layers at sizes that resemble a real model's (a parallel layer: windowed
+    attention with kept first keys beside a linear attention with a decay per head; an attention layer with a stretched
+    rotation, a sink and a gate per head; a second parallel layer; a second attention layer; each with routed experts
+    and a shared expert), and of the Vunepel layers that come closest (the library's other design with a recurrent mixer
+    beside attention and routed experts with a shared expert): same width and vocabulary, a delta-rule layer with the same
+    heads and state size where the parallel layer stands, an attention layer with as many score maps of the same size
+    under a chunk as long as the window, the same experts."""
+    import torch
+
+    from qwen_triton_b200 import QwenB200ForCausalLM, config_from_dict
+
+    peak, peak_source = peaks()
+    vocab, prompt_len = 32768, args.prompt_len
+    out = []
+    for size in REGUPEL_SIZES:
+        name, width, heads, kv_heads, dim, window, keep, rot, r_heads, r_dim, r_vdim, experts, top, ff, shared = size
+        if args.size and not name.startswith(args.size):
+            continue
+        moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared}}
+        attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window},
+                     "rot": {"base": 500000.0, "dims": rot, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+        left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window, "keep_first": keep}}
+        right = {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "decay": [1.0 - 2.0 ** (-1 - 7 * h / max(r_heads - 1, 1)) for h in range(r_heads)]}
+        parallel = {"left": left, "right": right, "left_scale": 0.6, "right_scale": 1.1}
+        regupel = {"architecture": "Regupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 3.0},
+                   "logit_scale": 1.0, "residual_mult": 0.3,
+                   "layers": [{"type": "parallel", "mixer": parallel, "mlp": moe}, {"type": "attention", "mixer": attention, "mlp": moe},
+                              {"type": "parallel", "mixer": parallel, "mlp": moe}, {"type": "attention", "mixer": attention, "mlp": moe}]}
+        v_moe = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 2.0}, "expert": {"ff": ff, "limit": 7.0},
+                 "shared": {"ff": shared, "limit": 7.0}}
+        v_heads, v_kv = max(1, heads // 2), max(1, kv_heads // 2)
+        v_attention = {"heads": v_heads, "kv_heads": v_kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "diff": 0.3,
+                       "rot": {"dims": rot, "base": 500000.0}, "mask": {"size": window}}
+        delta = {"heads": r_heads, "kv_heads": r_heads, "dim": r_dim, "vdim": r_vdim, "conv": 4, "ranks": {"decay": 64, "gate": 64}}
+        vunepel = {"architecture": "Vunepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+                   "layers": [{"type": "channel_delta", "mixer": delta, "mlp": v_moe}, {"type": "attention", "mixer": v_attention, "mlp": v_moe},
+                              {"type": "channel_delta", "mixer": delta, "mlp": v_moe}, {"type": "attention", "mixer": v_attention, "mlp": v_moe}]}
+        layers = 4
+        # weights a token multiplies with, per layer kind (the experts: the chosen ones and the shared one)
+        attn_w = width * ((heads + 2 * kv_heads) * dim + heads) + heads * dim * width
+        left_w = width * (heads + 2 * kv_heads) * dim + heads * dim * width
+        right_w = width * r_heads * (2 * r_dim + 2 * r_vdim) + r_heads * r_vdim * width
+        moe_token = 3 * width * (ff * top + shared) + width * experts
+        mixers = 2 * attn_w + 2 * (left_w + right_w)
+        token_weights = mixers + layers * moe_token
+        v_attn_w = width * (2 * v_heads + 2 * v_kv) * dim + width * v_kv * dim + v_heads * dim * width
+        v_delta_w = width * (2 * r_heads * r_dim + r_heads * r_vdim + r_heads + 128) + 64 * r_heads * (r_dim + r_vdim) + r_heads * r_vdim * width
+        v_mixers = 2 * v_attn_w + 2 * v_delta_w
+        v_token = v_mixers + layers * (moe_token + width)
+        entry = {"size": name, "layers": layers}
+
+        def moe_read(rows):
+            return 3 * width * (ff * min(experts, rows * top) + shared) + width * experts
+
+        def mean_keys(length, span, kept):
+            return sum(min(i + 1, span) + max(0, min(kept, i + 1 - span)) for i in range(length)) / length
+
+        def live_keys(context, span, kept):
+            return min(context, span + max(0, min(kept, context - span)))
+
+        # per arm: model, weights per token, weights a step of `rows` tokens reads, attention as (FLOPs per query and key, window,
+        # kept keys, cache bytes per key) per layer that has one, bytes of state read and written per sequence and step
+        arms = (("regupel", regupel, token_weights, lambda rows: mixers + layers * moe_read(rows),
+                 ((4 * heads * dim, window, keep, 4 * kv_heads * dim), (4 * heads * dim, window, 0, 4 * kv_heads * dim)) * 2,
+                 2 * r_heads * r_dim * r_vdim * 4 * 2),
+                ("vunepel", vunepel, v_token, lambda rows: v_mixers + layers * (moe_read(rows) + width),
+                 ((4 * 2 * v_heads * dim, window, 0, 2 * (2 * v_kv * dim + v_kv * dim)),) * 2, 2 * r_heads * r_dim * r_vdim * 4 * 2))
+        for label, raw, per_token, read_of, attention_layers, state_bytes in arms:
+            if args.arm and label != args.arm:
+                continue
+            model = QwenB200ForCausalLM.from_config(config_from_dict(raw), seed=1, dtype="bf16",
+                                                    max_tokens=64 * (prompt_len + 512), max_seq_len=prompt_len + 512,
+                                                    max_step_tokens=max(4096, prompt_len), chunk_tokens=prompt_len)
+            result = {}
+            if args.phase in (None, "prefill"):
+                ms = time_prefill(model, prompt_len, vocab, repeats=args.steps if args.phase else 5, warmup=args.warmup if args.phase else 3)
+                if label == "regupel":
+                    pairs = sum(f * prompt_len * mean_keys(prompt_len, span, kept) for f, span, kept, _ in attention_layers)
+                else:                      # a chunk's queries see the chunk's earlier keys
+                    pairs = sum(f * prompt_len * (min(prompt_len, span) / 2) for f, span, _, _ in attention_layers)
+                flops = 2 * prompt_len * (per_token + vocab * width / prompt_len) + pairs
+                result["prefill"] = {"tokens": prompt_len, "ms": round(ms, 3), "tokens_per_s": round(prompt_len * 1e3 / ms),
+                                     "tensor_fraction": round(flops / (ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)}
+            for batch in (8, 64):
+                if args.phase not in (None, f"decode{batch}"):
+                    continue
+                prompts = random_prompts(batch, prompt_len, vocab, 300 + batch)
+                ms, launches, clocks, context, steps = time_decode(model, prompts, args.steps, args.warmup, vocab,
+                                                                   args.min_seconds / 4, 256)
+                if label == "regupel":
+                    keys = sum(b * live_keys(context, span, kept) for _, span, kept, b in attention_layers)
+                else:
+                    keys = sum(b * (context % span) for _, span, _, b in attention_layers)
+                read = 2 * (read_of(batch) + vocab * width) + batch * (keys + state_bytes)
+                result[f"decode_batch{batch}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(batch * 1e3 / ms),
+                                                   "launches_per_step": round(launches / steps, 1), "steps": steps,
+                                                   "hbm_fraction": round(read / (ms * 1e-3) / (peak["hbm_gbs"] * 1e9), 4),
+                                                   "clocks": clocks}
+            entry[label] = result
+            print(f"[bench] {name} {label}: " + json.dumps({k: {a: b for a, b in v.items() if a != 'clocks'} for k, v in result.items()}),
+                  file=sys.stderr, flush=True)
+            del model
+            torch.cuda.empty_cache()
+        out.append(entry)
+    return {"workload": args.workload, "impl": "b200", "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
+            "config": {"prompt_len": prompt_len, "layers": 4, "vocab": vocab, "peaks": peak_source,
+                       "l2": "weights, caches and states of a step exceed L2 at every size but the smallest"},
+            "sizes": out}
+
+
 def time_prefill(model, tokens: int, vocab: int, repeats: int = 5, warmup: int = 3):
     import torch
     from qwen_triton_b200 import StepEntry
@@ -620,6 +743,8 @@ def run_workload(args) -> dict:
         return run_vunepel_layers(args)
     if args.workload == "bisodra-layers":
         return run_bisodra_layers(args)
+    if args.workload == "regupel-layers":
+        return run_regupel_layers(args)
     import torch
 
     from qwen_triton_b200 import QwenB200ForCausalLM, StepEntry, load_preset

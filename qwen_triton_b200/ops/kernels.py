@@ -48,7 +48,8 @@ _SIGNATURES = {
     },
     "linear_attention": {
         "qt_linear_attention_scan": [_c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int,
-                                     _c_int, _c_int, _c_int, _c_int, _c_ptr],
+                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+        "qt_linear_attention_prepare": [_c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr, _c_int, _c_ptr],
         "qt_linear_attention_gate_norm": [_c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr, _c_float, _c_float, _c_ptr, _c_int, _c_int,
                                           _c_int, _c_ptr],
     },
@@ -698,7 +699,17 @@ def linear_attention_scan(proj: GemmOut, at_q: int, at_k: int, at_v: int, decay:
         raise KernelError(f"linear_attention_scan: state {tuple(state.shape)} is not [slots, {heads}, {vdim}, {dim}], or {proj.rows} rows for {tokens} tokens")
     _call("linear_attention", "qt_linear_attention_scan", _ptr(proj.tensor), proj.n_splits, proj.split_stride, proj.cols, int(at_q), int(at_k),
           int(at_v), _ptr(decay), _ptr(state), _ptr(out), _ptr(ctx.seq_start), _ptr(ctx.slots), ctx.n_seqs, heads, int(dim), vdim,
-          1 if act else 0, _stream())
+          1 if act else 0, int(ctx.max_q_len), _stream())
+
+
+def linear_attention_prepare(proj: GemmOut, cols: int, out: torch.Tensor) -> GemmOut:
+    """out [T, cols] (float) = SiLU of the first ``cols`` columns of ``proj`` (float sums [*, T, all]): q, k and v of a step of
+    many tokens activated once, ahead of the recurrence."""
+    _need(proj.tensor, "proj", torch.float32)
+    _need(out, "out", torch.float32, (proj.rows, int(cols)))
+    _call("linear_attention", "qt_linear_attention_prepare", _ptr(proj.tensor), proj.n_splits, proj.split_stride, proj.cols, int(cols), _ptr(out),
+          proj.rows, _stream())
+    return GemmOut(out.view(1, proj.rows, int(cols)))
 
 
 def linear_attention_gate_norm(o: torch.Tensor, proj: GemmOut | None, at_gate: int, weight: torch.Tensor, eps: float, scale: float,
