@@ -41,29 +41,29 @@ __device__ __forceinline__ float la_raw(const LinAttnParams& p, size_t index) {
 }
 __device__ __forceinline__ float la_act(const LinAttnParams& p, float x) { return p.act ? x / (1.f + expf(-x)) : x; }
 
-// out[t, c] = SiLU(sum_s proj[s][t, c]) for the first `cols` columns of every row: q, k and v of a step of many tokens,
-// activated once where every block of the recurrence would otherwise activate its head's q and k again.
+// out[t, c] = SiLU(sum_s proj[s][t, c]) (or the sum itself) for the first `cols` columns of every row: q, k and v of a
+// step, summed and activated once where every block of the recurrence would otherwise activate its head's q and k again.
 __global__ void linear_attention_prepare_kernel(const float* __restrict__ proj, int n_splits, size_t split_stride, int proj_cols, int cols,
-                                                float* __restrict__ out, long long total) {
+                                                float* __restrict__ out, long long total, int act) {
     pdl_launch_dependents();
     pdl_wait();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const size_t at = (size_t)(i / cols) * proj_cols + (size_t)(i % cols);
         float x = proj[at];
         for (int s = 1; s < n_splits; ++s) x += proj[at + (size_t)s * split_stride];
-        out[i] = x / (1.f + expf(-x));
+        out[i] = act ? x / (1.f + expf(-x)) : x;
     }
 }
 
 extern "C" int qt_linear_attention_prepare(const float* proj, int n_splits, long long split_stride, int proj_cols, int cols, float* out, int n_tokens,
-                                           void* stream) {
+                                           int act, void* stream) {
     QT_REQUIRE(n_tokens >= 0 && cols > 0 && cols <= proj_cols && n_splits >= 1, "linear_attention_prepare: %d of %d columns", cols, proj_cols);
     if (n_tokens == 0) return QT_OK;
     const long long total = (long long)n_tokens * cols;
     long long blocks = (total + 255) / 256;
     if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
     launch_kernel(linear_attention_prepare_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, proj, n_splits, (size_t)split_stride, proj_cols,
-                  cols, out, total);
+                  cols, out, total, act);
     QT_CHECK_LAUNCH("linear_attention_prepare");
     return QT_OK;
 }
@@ -163,6 +163,87 @@ __global__ void __launch_bounds__(COLS * LA_LANES) linear_attention_scan_kernel(
             acc += __shfl_xor_sync(0xffffffffu, acc, 4);
             if (lane == 0 && live) p.out[((size_t)(t0 + tok) * p.heads + head) * p.vdim + col] = acc;
         }
+    }
+    if (live) {
+        if (vec) {
+#pragma unroll
+            for (int i = 0; i < RPL; i += 4)
+                if (row0 + i < p.dim) *reinterpret_cast<float4*>(state + row0 + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < RPL; ++i)
+                if (row0 + i < p.dim) state[row0 + i] = S[i];
+        }
+    }
+}
+
+// Steps in which no sequence brings more than a few tokens (one-token steps above all): nothing is staged or fetched
+// ahead, a thread reads its rows' q and k from the projection itself (the 32 columns of a block read the same ones, from
+// L1), so the kernel is short and light in registers and many blocks share an SM; its cost is the state's bytes.
+template <int RPL>
+__global__ void __launch_bounds__(32 * LA_LANES) linear_attention_step_kernel(const LinAttnParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int head = blockIdx.y, seq = blockIdx.z;
+    const int lane = threadIdx.x % LA_LANES, col = blockIdx.x * 32 + threadIdx.x / LA_LANES;
+    const int begin = p.seq_start[seq], end = p.seq_start[seq + 1];
+    if (begin >= end) return;
+    const float decay = p.decay[head];
+    const bool live = col < p.vdim;
+    float* state = p.state + (((size_t)p.slots[seq] * p.heads + head) * p.vdim + (live ? col : 0)) * p.dim;
+    const int row0 = lane * RPL;
+    const bool vec = p.dim % 4 == 0 && ((uintptr_t)p.state & 15) == 0;
+    float S[RPL];
+#pragma unroll
+    for (int i = 0; i < RPL; ++i) S[i] = 0.f;
+    if (live) {
+        if (vec) {
+#pragma unroll
+            for (int i = 0; i < RPL; i += 4)
+                if (row0 + i < p.dim) {
+                    const float4 v = *reinterpret_cast<const float4*>(state + row0 + i);
+                    S[i] = v.x; S[i + 1] = v.y; S[i + 2] = v.z; S[i + 3] = v.w;
+                }
+        } else {
+#pragma unroll
+            for (int i = 0; i < RPL; ++i)
+                if (row0 + i < p.dim) S[i] = state[row0 + i];
+        }
+    }
+    const bool quads = p.n_splits == 1 && p.dim % 4 == 0 && p.at_q % 4 == 0 && p.at_k % 4 == 0 && p.proj_cols % 4 == 0 && ((uintptr_t)p.proj & 15) == 0;
+    for (int t = begin; t < end; ++t) {
+        const size_t row = (size_t)t * p.proj_cols;
+        const float v = live ? la_act(p, la_raw(p, row + p.at_v + (size_t)head * p.vdim + col)) : 0.f;
+        float q[RPL], k[RPL];
+        const size_t q_at = row + p.at_q + (size_t)head * p.dim + row0, k_at = row + p.at_k + (size_t)head * p.dim + row0;
+        if (quads) {                                        // 16-byte loads of a row that is finished and aligned
+#pragma unroll
+            for (int i = 0; i < RPL; i += 4) {
+                const bool has = row0 + i < p.dim;
+                const float4 q4 = has ? __ldg(reinterpret_cast<const float4*>(p.proj + q_at + i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 k4 = has ? __ldg(reinterpret_cast<const float4*>(p.proj + k_at + i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                q[i] = q4.x; q[i + 1] = q4.y; q[i + 2] = q4.z; q[i + 3] = q4.w;
+                k[i] = k4.x; k[i + 1] = k4.y; k[i + 2] = k4.z; k[i + 3] = k4.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < RPL; ++i) {                 // every load of the token ahead of its arithmetic
+                const bool has = row0 + i < p.dim;
+                q[i] = has ? la_raw(p, q_at + i) : 0.f;
+                k[i] = has ? la_raw(p, k_at + i) : 0.f;
+            }
+        }
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < RPL; i += 2) {
+            S[i] = fmaf(decay, S[i], la_act(p, k[i]) * v);             a0 = fmaf(S[i], la_act(p, q[i]), a0);
+            S[i + 1] = fmaf(decay, S[i + 1], la_act(p, k[i + 1]) * v); a1 = fmaf(S[i + 1], la_act(p, q[i + 1]), a1);
+        }
+        float acc = a0 + a1;
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+        if (lane == 0 && live) p.out[((size_t)t * p.heads + head) * p.vdim + col] = acc;
     }
     if (live) {
         if (vec) {
@@ -289,6 +370,14 @@ extern "C" int qt_linear_attention_scan(const float* proj, int n_splits, long lo
     // blocks of 32 columns where they fill the machine twice over (many sequences: every block stages its head's q and k
     // itself), else of 16, so that one prompt still gives most SMs a block
     const bool wide = (long long)((vdim + 31) / 32) * heads * n_seqs >= 2LL * sm_count();
+    if (max_q_len <= 4) {                                  // few tokens a sequence: the short kernel
+        const dim3 grid((vdim + 31) / 32, heads, n_seqs), block(32 * LA_LANES);
+        if (dim <= LA_LANES * 8) launch_kernel(linear_attention_step_kernel<8>, grid, block, 0, s, p);
+        else if (dim <= LA_LANES * 16) launch_kernel(linear_attention_step_kernel<16>, grid, block, 0, s, p);
+        else launch_kernel(linear_attention_step_kernel<32>, grid, block, 0, s, p);
+        QT_CHECK_LAUNCH("linear_attention_scan");
+        return QT_OK;
+    }
     // long portions of few sequences, with a head's rows within what 32 lanes hold four at a time: a warp per column
     static const bool warp_form = [] { const char* env = getenv("QT_B200_LINEAR_WARP"); return !(env && env[0] == '0'); }();
     if (warp_form && max_q_len >= 64 && dim > 64 && (long long)((vdim + 15) / 16) * heads * n_seqs < 2LL * sm_count()) {

@@ -49,7 +49,7 @@ _SIGNATURES = {
     "linear_attention": {
         "qt_linear_attention_scan": [_c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int,
                                      _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
-        "qt_linear_attention_prepare": [_c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr, _c_int, _c_ptr],
+        "qt_linear_attention_prepare": [_c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr],
         "qt_linear_attention_gate_norm": [_c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr, _c_float, _c_float, _c_ptr, _c_int, _c_int,
                                           _c_int, _c_ptr],
     },
@@ -702,13 +702,13 @@ def linear_attention_scan(proj: GemmOut, at_q: int, at_k: int, at_v: int, decay:
           1 if act else 0, int(ctx.max_q_len), _stream())
 
 
-def linear_attention_prepare(proj: GemmOut, cols: int, out: torch.Tensor) -> GemmOut:
-    """out [T, cols] (float) = SiLU of the first ``cols`` columns of ``proj`` (float sums [*, T, all]): q, k and v of a step of
-    many tokens activated once, ahead of the recurrence."""
+def linear_attention_prepare(proj: GemmOut, cols: int, out: torch.Tensor, act: bool = True) -> GemmOut:
+    """out [T, cols] (float) = SiLU (with ``act``) of the first ``cols`` columns of ``proj`` (float sums [*, T, all]): q, k
+    and v of a step summed and activated once, ahead of the recurrence."""
     _need(proj.tensor, "proj", torch.float32)
     _need(out, "out", torch.float32, (proj.rows, int(cols)))
     _call("linear_attention", "qt_linear_attention_prepare", _ptr(proj.tensor), proj.n_splits, proj.split_stride, proj.cols, int(cols), _ptr(out),
-          proj.rows, _stream())
+          proj.rows, 1 if act else 0, _stream())
     return GemmOut(out.view(1, proj.rows, int(cols)))
 
 

@@ -37,7 +37,6 @@ from .linear import Linear
 
 _UNIT_EPS = 1e-6      # inside the root of the unit norms of q and k
 _FEW_TOKENS = 4       # steps in which no sequence brings more tokens run the recurrence token by token
-_PREPARE_TOKENS = 32  # linear attention: steps in which a sequence brings as many tokens activate q, k and v in a pass of their own
 
 
 @register_mixer("gated_delta_rule")
@@ -270,12 +269,9 @@ class LinearAttention:
         ws = self.runtime.workspace
         proj = self.proj(x)
         read = ws.view("linattn.read", tokens, self.heads, self.vdim)
-        if self.act and ctx.max_q_len >= _PREPARE_TOKENS:
-            # many tokens: q, k and v are activated once, not by every block of the recurrence that reads them
-            ready = kernels.linear_attention_prepare(proj, self.at_gate, ws.view("linattn.qkv", tokens, self.at_gate))
-            kernels.linear_attention_scan(ready, 0, self.at_k, self.at_v, self.decay, cache.state, read, ctx, self.dim, False)
-        else:
-            kernels.linear_attention_scan(proj, 0, self.at_k, self.at_v, self.decay, cache.state, read, ctx, self.dim, self.act)
+        # q, k and v are summed and activated once, not by every block of the recurrence that reads them
+        ready = kernels.linear_attention_prepare(proj, self.at_gate, ws.view("linattn.qkv", tokens, self.at_gate), self.act)
+        kernels.linear_attention_scan(ready, 0, self.at_k, self.at_v, self.decay, cache.state, read, ctx, self.dim, False)
         normed = ws.view("linattn.normed", tokens, self.heads * self.vdim)
         kernels.linear_attention_gate_norm(read.view(tokens, self.heads * self.vdim), proj if self.gated else None, self.at_gate, self.norm,
                                            self.eps, 1.0, normed)
