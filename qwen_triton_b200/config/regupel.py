@@ -196,9 +196,10 @@ class RegupelConfig:
             if m is not None and (min(m.ff, m.experts, m.top) <= 0 or m.top > m.experts or (m.shared_ff is not None and m.shared_ff <= 0)):
                 problems.append(f"{where}.mlp: ff={m.ff}, {m.top} of {m.experts} experts, shared ff={m.shared_ff}")
             if layer.weights_of is not None:
+                # a layer may name one that itself runs another's tensors: the owner is where that chain ends
                 owner = self.layers[layer.weights_of] if 0 <= layer.weights_of < index else None
-                if owner is None or owner.weights_of is not None:
-                    problems.append(f"{where}: weights_of={layer.weights_of} must name an earlier layer with tensors of its own")
+                if owner is None:
+                    problems.append(f"{where}: weights_of={layer.weights_of} must name an earlier layer")
                 elif (owner.type, owner.attention, owner.linear, owner.left_scale, owner.right_scale, owner.mlp) != \
                         (layer.type, layer.attention, layer.linear, layer.left_scale, layer.right_scale, layer.mlp):
                     problems.append(f"{where}: its entry differs from that of layer {layer.weights_of}, whose tensors it uses")
@@ -268,7 +269,8 @@ class RegupelConfig:
         layers, schedule, at = [], [], {}
         for index, layer in enumerate(self.layers):
             if layer.weights_of is not None:
-                schedule.append(LayerCall(layer=at[layer.weights_of]))
+                at[index] = at[layer.weights_of]          # the owner's, also where the named layer runs another's itself
+                schedule.append(LayerCall(layer=at[index]))
                 continue
             if layer.type == "attention":
                 mixer = self._attention_part(layer.attention, False, init_std)

@@ -54,6 +54,13 @@ def test_the_spec_runs_a_layer_twice_with_one_set_of_tensors():
     assert "l0.mlp.shared.gate_weight" not in names and "l1.mix.left.sink" not in names and "l1.mix.left.g" not in names
 
 
+def test_a_layer_may_name_one_that_runs_another_layers_tensors():
+    raw = copy.deepcopy(RAW)
+    raw["layers"].append({**copy.deepcopy(raw["layers"][2]), "weights_of": 2})
+    spec = config_from_dict(raw).model_spec()
+    assert [call.layer for call in spec.schedule] == [0, 1, 0, 0] and len(spec.layers) == 2
+
+
 def test_what_may_be_absent():
     raw = copy.deepcopy(RAW)
     del raw["layers"][0]["mixer"]["mask"], raw["layers"][0]["mixer"]["rot"]["scaling"], raw["layers"][0]["mlp"]["shared"]
@@ -77,6 +84,7 @@ def test_what_may_be_absent():
     (lambda r: r["layers"][1]["mixer"]["right"].update(decay=[0.5, 0.9, 1.5]), "decays"),
     (lambda r: r["layers"][0]["mlp"]["router"].update(top=4), "of 3 experts"),
     (lambda r: r["layers"][2].update(weights_of=2), "earlier layer"),
+    (lambda r: r["layers"][2].update(weights_of=1), "differs"),
     (lambda r: r["layers"][2]["mixer"].update(scale=0.4), "differs"),
     (lambda r: r["layers"][0]["mixer"]["rot"].update(dims=3), "even"),
     (lambda r: r.pop("vocab"), "vocab"),
