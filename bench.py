@@ -461,12 +461,12 @@ def run_regupel_layers(args) -> dict:
             continue
         moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared}}
         attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window},
-                     "rot": {"base": 500000.0, "dims": rot, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+                     "rot": {"base": 1000000.0, "dims": rot, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 8192}}}
         left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window, "keep_first": keep}}
         right = {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "decay": [1.0 - 2.0 ** (-1 - 7 * h / max(r_heads - 1, 1)) for h in range(r_heads)]}
-        parallel = {"left": left, "right": right, "left_scale": 0.6, "right_scale": 1.1}
-        regupel = {"architecture": "Regupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 3.0},
-                   "logit_scale": 1.0, "residual_mult": 0.3,
+        parallel = {"left": left, "right": right, "left_scale": 0.7, "right_scale": 1.2}
+        regupel = {"architecture": "Regupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
+                   "logit_scale": 1.0, "residual_mult": 0.4,
                    "layers": [{"type": "parallel", "mixer": parallel, "mlp": moe}, {"type": "attention", "mixer": attention, "mlp": moe},
                               {"type": "parallel", "mixer": parallel, "mlp": moe}, {"type": "attention", "mixer": attention, "mlp": moe}]}
         v_moe = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 2.0}, "expert": {"ff": ff, "limit": 7.0},

@@ -32,11 +32,11 @@ def draw_attention(rng, left: bool) -> dict:
             mixer["mask"]["keep_first"] = rng.choice([0, 0, 1, 3, 20, 64, 70])
     if not left and rng.random() < 0.85:
         dims = rng.choice([d for d in (2, 4, 8, 16, dim) if d <= dim and d % 2 == 0])
-        mixer["rot"] = {"dims": dims, "base": rng.choice([100.0, 10000.0, 500000.0])}
+        mixer["rot"] = {"dims": dims, "base": rng.choice([100.0, 10000.0, 300000.0])}
         if rng.random() < 0.6:
             low = rng.choice([1.0, 2.0])
-            mixer["rot"]["scaling"] = {"factor": rng.choice([2.0, 8.0, 40.0]), "low": low, "high": low + rng.choice([1.0, 3.0]),
-                                       "original": rng.choice([16, 100, 2048])}
+            mixer["rot"]["scaling"] = {"factor": rng.choice([2.0, 6.0, 40.0]), "low": low, "high": low + rng.choice([1.0, 3.0]),
+                                       "original": rng.choice([16, 100, 1024])}
     return mixer
 
 
@@ -62,12 +62,12 @@ def draw(seed: int) -> dict:
             right = {"heads": heads, "dim": rng.choice([4, 10, 16, 64, 72, 128, 200]), "vdim": rng.choice([4, 8, 20, 32, 33, 64]),
                      "decay": [rng.choice([0.0, 1.0, 0.5, round(rng.uniform(0.8, 0.999), 4)]) for _ in range(heads)]}
             layers.append({"type": "parallel", "mlp": mlp,
-                           "mixer": {"left": draw_attention(rng, True), "right": right, "left_scale": rng.choice([1.0, 0.6, 0.3]),
-                                     "right_scale": rng.choice([1.0, 1.1, 2.0])}})
+                           "mixer": {"left": draw_attention(rng, True), "right": right, "left_scale": rng.choice([1.0, 0.7, 0.35]),
+                                     "right_scale": rng.choice([1.0, 1.2, 2.0])}})
         owners.append(index)
     return {"architecture": "Regupel", "vocab": rng.randint(30, 300), "width": width, "norm": {"eps": rng.choice([1e-6, 1e-5, 1e-3])},
-            "embedding": {"scale": rng.choice([1.0, 3.0, 11.5])}, "logit_scale": rng.choice([1.0, 2.0, 0.7]),
-            "residual_mult": rng.choice([1.0, 0.3, 0.5]), "layers": layers}
+            "embedding": {"scale": rng.choice([1.0, 2.5, 11.5])}, "logit_scale": rng.choice([1.0, 1.5, 0.7]),
+            "residual_mult": rng.choice([1.0, 0.25, 0.5]), "layers": layers}
 
 
 @pytest.mark.parametrize("dtype", ("fp32", "bf16"))
